@@ -1,0 +1,147 @@
+/*
+ * mqmoe.h - C ABI of libmqmoe.so: the MoE block of mini-qwen-llm (top-k router, expert-sorted
+ * permute, grouped SwiGLU expert GEMM in bf16 and W4A16, weighted unpermute-combine) as
+ * hand-written sm_100a CUDA kernels.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name starts with "h_";
+ *   - every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = legacy
+ *     default stream), allocates nothing and keeps no state between calls (tensor maps are
+ *     rebuilt per call on the host);
+ *   - matrices are dense row-major; element types are given by mq_dtype;
+ *   - the return value is an mq_status; a non-zero value means nothing was launched
+ *     (argument checks) or the launch itself failed.  Conditions only the device can see
+ *     (a bounded wait that ran out) are written to the optional `d_status` word and never
+ *     trap;
+ *   - "slot" = one (token, k) pair; S = T * top_k slots; slots are stored expert-sorted.
+ *
+ * Each entry point names the reference interface it replaces (paths inside the
+ * mini-qwen-llm project).
+ */
+#ifndef MQMOE_H
+#define MQMOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { MQ_F32 = 0, MQ_BF16 = 1, MQ_F16 = 2 } mq_dtype;
+
+typedef enum {
+  MQ_OK = 0,
+  MQ_ERR_INVALID_ARGUMENT = 1,   /* null pointer, negative size, misaligned pointer */
+  MQ_ERR_UNSUPPORTED_SHAPE = 2,  /* a size outside what the kernels cover (see each call) */
+  MQ_ERR_WORKSPACE_TOO_SMALL = 3,
+  MQ_ERR_LAUNCH_FAILED = 4,      /* cudaGetLastError() after the launch was not cudaSuccess */
+  MQ_ERR_DRIVER_ENTRY = 5        /* cuTensorMapEncodeTiled could not be resolved or failed */
+} mq_status;
+
+/* bits of the device status word */
+#define MQ_DEV_WAIT_EXPIRED 1u   /* a bounded mbarrier wait gave up; the output is invalid */
+
+int mq_version(void);
+const char* mq_status_string(int status);
+/* cudaGetErrorString of the last launch failure seen by this library on this thread. */
+const char* mq_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Router.  Replaces moe_router (mini_qwen/kernels/moe_router.py:7-22): fp32 logits = x . w^T
+ * (+ bias), fp32 softmax over the E experts, the K largest scores in descending order; equal
+ * scores are ordered by ascending expert id.  renormalize != 0 additionally divides the K
+ * weights by their sum (mini_qwen/model/layers/moe.py:55-56).
+ *   x [T,H] (x_dtype), w [E,H] (w_dtype), bias fp32 [E] or NULL,
+ *   logits_ws fp32 [T,E] caller-provided workspace (overwritten),
+ *   ids64 int64 [T,K] and/or ids32 int32 [T,K] (either may be NULL, not both),
+ *   weights fp32 [T,K].
+ * Limits: 1 <= K <= E <= 1024, K <= 32.
+ */
+int mq_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
+                   int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
+                   float* logits_ws, int64_t* ids64, int32_t* ids32, float* weights,
+                   void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Permute plan.  Replaces the index work of moe_permute / moe_unpermute
+ * (mini_qwen/kernels/moe_permute.py:22-27, moe_unpermute.py:23-25): a stable counting sort of
+ * the S = T*K flat slots by expert id.
+ *   ids: [T,K] int64 (ids_are_64 != 0) or int32, every id in [0, E);
+ *   perm  int32 [S]: perm[p] = flat slot t*K+k stored at sorted position p;
+ *   inv   int32 [S]: inv[t*K+k] = p;
+ *   offsets64 int64 [E+1] and/or offsets32 int32 [E+1] (either may be NULL): exclusive
+ *   prefix sum of per-expert slot counts;
+ *   workspace: mq_permute_workspace_bytes(S, E) bytes.
+ * Limits: E <= 1024, S < 2^31.
+ */
+size_t mq_permute_workspace_bytes(int64_t S, int64_t E);
+int mq_permute_plan(const void* ids, int ids_are_64, int64_t T, int64_t K, int64_t E,
+                    int32_t* perm, int32_t* inv, int64_t* offsets64, int32_t* offsets32,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Row gather of moe_permute (moe_permute.py:30-31): out[p,:] = x[perm[p] / K, :].
+ * H * sizeof(dtype) must be a multiple of 16 and the pointers 16-byte aligned. */
+int mq_gather_rows(const void* x, int dtype, const int32_t* perm, int64_t S, int64_t K, int64_t H,
+                   void* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Unpermute + weighted combine.  Replaces moe_unpermute (mini_qwen/kernels/moe_unpermute.py:
+ * 20-31): out[t,:] = cast(sum_k weights[t,k] * float(rows[inv[t*K+k],:])), products and the
+ * sum in fp32, k ascending.  rows [S,H] and out [T,H] have type `dtype`.
+ */
+int mq_unpermute_combine(const void* rows, int dtype, const float* weights, const int32_t* inv,
+                         int64_t T, int64_t K, int64_t H, void* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Grouped GEMM, one projection.  Replaces moe_grouped_gemm / _moe_grouped_gemm_oracle
+ * (mini_qwen/kernels/moe_grouped_gemm.py:17-37,115-156): for every expert e,
+ * out[off[e]:off[e+1], :] = a[off[e]:off[e+1], :] . w[e]^T with fp32 accumulation.
+ *   a [S,Kd], w [E,N,Kd], out [S,N], all of type `dtype`; offsets int32 [E+1].
+ * Rows of `out` that belong to no expert are not written.
+ * bf16 with Kd % 64 == 0 and N % 64 == 0 runs on the tcgen05/TMEM kernel, everything else on
+ * a generic tiled kernel (Kd % 8 == 0 for 16-bit types, % 4 for fp32).
+ */
+int mq_grouped_gemm(const void* a, const void* w, const int32_t* offsets,
+                    int64_t S, int64_t E, int64_t N, int64_t Kd, int dtype,
+                    void* out, int32_t* d_status, void* stream);
+
+/* Fused gate/up projection with SwiGLU. Replaces _ExpertMLP's first half
+ * (mini_qwen/model/layers/moe.py:24-25) for all experts at once:
+ *   h[s,:] = round(round(silu(round(a[s,:] . wg[e]^T))) * round(a[s,:] . wu[e]^T)),
+ * every round() to `dtype`, as the per-expert nn.Linear path rounds.
+ *   a [S,H], w_gate_up [E, 2*I, H] (gate rows first, then up rows), h [S,I].
+ */
+int mq_grouped_swiglu(const void* a, const void* w_gate_up, const int32_t* offsets,
+                      int64_t S, int64_t E, int64_t I, int64_t H, int dtype,
+                      void* h, int32_t* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * W4A16 linear.  Replaces w4a16_gemm (mini_qwen/kernels/w4a16_gemm.py:8-15,194-247) and,
+ * with E > 1, the per-expert calls LinearW4A16.forward makes from the expert loop
+ * (mini_qwen/model/layers/linear_w4a16.py:31-36):
+ *   out[r, n] = bf16( sum_k x[r,k] * (q[e][k,n] - z[e][k/g, n]) * s[e][k/g, n] )
+ * for rows r in [off[e], off[e+1]).
+ *   x bf16 [S,Kd]; qweight int32 [E, Kd/8, N] (nibble i of word [j,n] = q[8j+i, n]);
+ *   scales bf16 [E, Kd/g, N]; qzeros int32 [E, Kd/g, N/8] (nibble i of word [G,m] = z[G, 8m+i]);
+ *   offsets int32 [E+1] (for a single linear: E = 1, offsets = {0, M}); out bf16 [S,N].
+ * Limits: g % 32 == 0, Kd % g == 0, N % 8 == 0.
+ */
+int mq_w4a16_grouped_gemm(const void* x, const int32_t* qweight, const void* scales,
+                          const int32_t* qzeros, const int32_t* offsets,
+                          int64_t S, int64_t E, int64_t N, int64_t Kd, int64_t group_size,
+                          void* out, void* stream);
+
+/* Fused W4A16 gate/up projection with SwiGLU (bf16 rounding after gate, silu, up and the
+ * product, as LinearW4A16 returns bf16).  Both projections share shapes: Kd = H, N = I. */
+int mq_w4a16_grouped_swiglu(const void* x,
+                            const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
+                            const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
+                            const int32_t* offsets,
+                            int64_t S, int64_t E, int64_t I, int64_t H, int64_t group_size,
+                            void* h, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MQMOE_H */

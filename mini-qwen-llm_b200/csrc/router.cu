@@ -1,0 +1,277 @@
+// Top-k router: fp32 logits -> fp32 softmax -> K largest scores (ties: lower expert id).
+// Follows mini_qwen/kernels/moe_router.py:19-22 and the renormalisation of
+// mini_qwen/model/layers/moe.py:55-56.
+//
+// Two launches: a logits kernel (x . w^T in fp32 FMA; products of 16-bit inputs are exact in
+// fp32, so the only rounding is the running sum) into a [T,E] fp32 workspace, then one warp per
+// token for softmax + selection.  Tensor cores are deliberately not used for the logits: expert
+// ids must equal those of an fp32 reference, and the adjacent-score gaps are a few fp32 ulp.
+#include "common.cuh"
+
+namespace mq {
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// 8 consecutive elements starting at element index i (i % 8 == 0, base 16-byte aligned), as fp32.
+__device__ __forceinline__ void load8(const void* p, int dt, size_t i, float (&v)[8]) {
+  if (dt == MQ_F32) {
+    const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    float4 a = __ldg(q), b = __ldg(q + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    uint4 r = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p) + i));
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (dt == MQ_BF16) {
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      } else {
+        __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+        float2 f = __half22float2(h);
+        v[2 * j] = f.x; v[2 * j + 1] = f.y;
+      }
+    }
+  }
+}
+
+// 8 elements with bounds and alignment handled element by element (any H).
+__device__ __forceinline__ void load8_safe(const void* p, int dt, size_t row_base, int64_t k, int64_t H,
+                                           bool vec_ok, float (&v)[8]) {
+  if (vec_ok && k + 8 <= H) {
+    load8(p, dt, row_base + k, v);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = (k + j < H) ? load_as_float(p, dt, row_base + k + j) : 0.0f;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tiled logits: CTA = 32 tokens x 64 experts, 128 threads, each thread 4 tokens x 4 experts.
+constexpr int R_TM = 32, R_TE = 64, R_KC = 32, R_THREADS = 128;
+
+__global__ void __launch_bounds__(R_THREADS)
+router_logits_tiled(const void* __restrict__ x, int xdt, const void* __restrict__ w, int wdt,
+                    int64_t T, int64_t H, int64_t E, int vec_ok, float* __restrict__ logits) {
+  __shared__ __align__(16) float xs[R_KC][R_TM];
+  __shared__ __align__(16) float ws[R_KC][R_TE];
+
+  const int tid = threadIdx.x;
+  const int64_t t0 = (int64_t)blockIdx.x * R_TM;
+  const int64_t e0 = (int64_t)blockIdx.y * R_TE;
+  const int tg = tid >> 4, eg = tid & 15;
+
+  // loader roles: x tile: token tid%32, k part tid/32 (8 wide); w tile: expert tid%64, k part tid/64 (16 wide)
+  const int lx_tok = tid & 31, lx_k = (tid >> 5) * 8;
+  const int lw_e = tid & 63, lw_k = (tid >> 6) * 16;
+  const bool x_in = t0 + lx_tok < T;
+  const bool w_in = e0 + lw_e < E;
+  const size_t x_row = (size_t)(t0 + lx_tok) * H;
+  const size_t w_row = (size_t)(e0 + lw_e) * H;
+
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+  float px[8], pw0[8], pw1[8];
+  auto fetch = [&](int64_t k0) {
+    if (x_in) load8_safe(x, xdt, x_row, k0 + lx_k, H, vec_ok, px);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) px[j] = 0.0f;
+    }
+    if (w_in) {
+      load8_safe(w, wdt, w_row, k0 + lw_k, H, vec_ok, pw0);
+      load8_safe(w, wdt, w_row, k0 + lw_k + 8, H, vec_ok, pw1);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { pw0[j] = 0.0f; pw1[j] = 0.0f; }
+    }
+  };
+
+  fetch(0);
+  for (int64_t k0 = 0; k0 < H; k0 += R_KC) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      xs[lx_k + j][lx_tok] = px[j];
+      ws[lw_k + j][lw_e] = pw0[j];
+      ws[lw_k + 8 + j][lw_e] = pw1[j];
+    }
+    __syncthreads();
+    if (k0 + R_KC < H) fetch(k0 + R_KC);
+#pragma unroll
+    for (int k = 0; k < R_KC; ++k) {
+      float4 xv = *reinterpret_cast<const float4*>(&xs[k][4 * tg]);
+      float4 wv = *reinterpret_cast<const float4*>(&ws[k][4 * eg]);
+      const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
+      const float wa[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wa[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int64_t t = t0 + 4 * tg + i;
+    if (t >= T) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int64_t e = e0 + 4 * eg + j;
+      if (e < E) logits[t * E + e] = acc[i][j];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Skinny logits (few tokens): one CTA per expert, each warp takes blocks of 8 tokens; the lanes
+// split H, partial sums meet in a shuffle tree.
+__global__ void __launch_bounds__(128)
+router_logits_skinny(const void* __restrict__ x, int xdt, const void* __restrict__ w, int wdt,
+                     int64_t T, int64_t H, int64_t E, int vec_ok, float* __restrict__ logits) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t e = blockIdx.x;
+  const size_t w_row = (size_t)e * H;
+  for (int64_t tb = (int64_t)warp * 8; tb < T; tb += 4 * 8) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    for (int64_t k = (int64_t)lane * 8; k < H; k += 32 * 8) {
+      float wv[8];
+      load8_safe(w, wdt, w_row, k, H, vec_ok, wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (tb + i < T) {
+          float xv[8];
+          load8_safe(x, xdt, (size_t)(tb + i) * H, k, H, vec_ok, xv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i] = fmaf(xv[j], wv[j], acc[i]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float v = acc[i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && tb + i < T) logits[(tb + i) * E + e] = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// One warp per token: softmax over E logits, then K rounds of warp arg-max on (score, -id).
+template <int EPL>
+__global__ void __launch_bounds__(128)
+router_softmax_topk(const float* __restrict__ logits, const float* __restrict__ bias,
+                    int64_t T, int E, int K, int renorm,
+                    int64_t* __restrict__ ids64, int32_t* __restrict__ ids32, float* __restrict__ weights) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= T) return;
+
+  float s[EPL];
+  float m = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    int e = lane + 32 * j;
+    float v = -INFINITY;
+    if (e < E) {
+      v = logits[t * E + e];
+      if (bias != nullptr) v += bias[e];
+    }
+    s[j] = v;
+    m = fmaxf(m, v);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    int e = lane + 32 * j;
+    float p = (e < E) ? expf(s[j] - m) : 0.0f;
+    s[j] = p;
+    sum += p;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) s[j] = (lane + 32 * j < E) ? s[j] / sum : -1.0f;  // scores >= 0; -1 = absent
+
+  uint32_t taken = 0;
+  float my_w = 0.0f;
+  int my_id = 0;
+  float wsum = 0.0f;
+  for (int k = 0; k < K; ++k) {
+    float best = -2.0f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      // ascending j = ascending id within the lane, strict > keeps the lower id on ties
+      if (!((taken >> j) & 1u) && s[j] > best) { best = s[j]; best_e = lane + 32 * j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
+    if (lane == k) { my_w = best; my_id = best_e; }
+    wsum += best;
+  }
+  if (lane < K) {
+    float wv = renorm ? my_w / wsum : my_w;
+    weights[t * K + lane] = wv;
+    if (ids64 != nullptr) ids64[t * K + lane] = my_id;
+    if (ids32 != nullptr) ids32[t * K + lane] = my_id;
+  }
+}
+
+template <int EPL>
+void launch_topk(const float* logits, const float* bias, int64_t T, int E, int K, int renorm,
+                 int64_t* ids64, int32_t* ids32, float* weights, cudaStream_t st) {
+  unsigned blocks = (unsigned)((T + 3) / 4);
+  router_softmax_topk<EPL><<<blocks, 128, 0, st>>>(logits, bias, T, E, K, renorm, ids64, ids32, weights);
+}
+
+}  // namespace
+}  // namespace mq
+
+extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
+                              int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
+                              float* logits_ws, int64_t* ids64, int32_t* ids32, float* weights,
+                              void* stream) {
+  using namespace mq;
+  if (T < 0 || H <= 0 || E <= 0 || K <= 0) return MQ_ERR_INVALID_ARGUMENT;
+  if (!valid_dtype(x_dtype) || !valid_dtype(w_dtype)) return MQ_ERR_INVALID_ARGUMENT;
+  if (K > E || E > 1024 || K > 32) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (T == 0) return MQ_OK;
+  if (!x || !w || !logits_ws || !weights || (!ids64 && !ids32)) return MQ_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+  // vector loads need 16-byte rows: H a multiple of 8 elements and aligned bases
+  int vec_ok = (H % 8 == 0) && aligned16(x) && aligned16(w);
+
+  if (T <= 64) {
+    router_logits_skinny<<<(unsigned)E, 128, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, vec_ok, logits_ws);
+  } else {
+    dim3 grid((unsigned)((T + R_TM - 1) / R_TM), (unsigned)((E + R_TE - 1) / R_TE));
+    router_logits_tiled<<<grid, R_THREADS, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, vec_ok, logits_ws);
+  }
+  int rc = check_launch();
+  if (rc != MQ_OK) return rc;
+
+  int e = (int)E, k = (int)K;
+  if (E <= 32) launch_topk<1>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else if (E <= 64) launch_topk<2>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else if (E <= 128) launch_topk<4>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else if (E <= 256) launch_topk<8>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else if (E <= 512) launch_topk<16>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else launch_topk<32>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  return check_launch();
+}

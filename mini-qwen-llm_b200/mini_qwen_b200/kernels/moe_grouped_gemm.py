@@ -1,0 +1,60 @@
+"""Grouped expert GEMM. Same call as ``mini_qwen/kernels/moe_grouped_gemm.py:115-156``."""
+from __future__ import annotations
+
+import torch
+
+from .. import _cabi
+
+
+def _status_word(dev) -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device=dev)
+
+
+def _offsets32(expert_offsets: torch.Tensor) -> torch.Tensor:
+    return expert_offsets if expert_offsets.dtype == torch.int32 else expert_offsets.to(torch.int32)
+
+
+def moe_grouped_gemm(
+    permuted_hidden: torch.Tensor,   # [num_tokens * top_k, hidden_dim]
+    expert_weights: torch.Tensor,    # [num_experts, out_dim, hidden_dim]
+    expert_offsets: torch.Tensor,    # [num_experts + 1]
+) -> torch.Tensor:
+    """``out[s:t] = permuted_hidden[s:t] @ expert_weights[e].T`` per expert, fp32 accumulation.
+
+    Unlike the reference there is no CPU branch (``moe_grouped_gemm.py:124-125``): CPU tensors
+    are an error.  Rows covered by no expert are zero, as in the reference's oracle."""
+    _cabi.require_cuda(permuted_hidden, expert_weights, expert_offsets)
+    assert permuted_hidden.dim() == 2 and expert_weights.dim() == 3
+    assert permuted_hidden.dtype == expert_weights.dtype, "activations and weights must share a dtype"
+    E, D, H = expert_weights.shape
+    assert permuted_hidden.shape[1] == H and expert_offsets.numel() == E + 1
+    a = permuted_hidden.contiguous()
+    w = expert_weights.contiguous()
+    S = a.shape[0]
+    out = torch.zeros(S, D, dtype=a.dtype, device=a.device)
+    status = _status_word(a.device)
+    rc = _cabi.load().mq_grouped_gemm(_cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(_offsets32(expert_offsets)), S, E, D, H,
+                                      _cabi.dtype_code(a), _cabi.ptr(out), _cabi.ptr(status),
+                                      _cabi.stream_ptr(a.device))
+    _cabi.check(rc, "mq_grouped_gemm")
+    return out
+
+
+def moe_grouped_swiglu(permuted_hidden: torch.Tensor, gate_up_weights: torch.Tensor,
+                       expert_offsets: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``h[s:t] = silu(x @ Wg[e].T) * (x @ Wu[e].T)`` with a rounding to the tensor dtype after
+    every op, as the per-expert module path rounds.  ``gate_up_weights`` is [E, 2I, H]: gate
+    rows first, then up rows."""
+    _cabi.require_cuda(permuted_hidden, gate_up_weights, expert_offsets)
+    E, I2, H = gate_up_weights.shape
+    assert I2 % 2 == 0 and permuted_hidden.shape[1] == H
+    a = permuted_hidden.contiguous()
+    S = a.shape[0]
+    h = torch.zeros(S, I2 // 2, dtype=a.dtype, device=a.device)
+    if status is None:
+        status = _status_word(a.device)
+    rc = _cabi.load().mq_grouped_swiglu(_cabi.ptr(a), _cabi.ptr(gate_up_weights), _cabi.ptr(_offsets32(expert_offsets)),
+                                        S, E, I2 // 2, H, _cabi.dtype_code(a), _cabi.ptr(h), _cabi.ptr(status),
+                                        _cabi.stream_ptr(a.device))
+    _cabi.check(rc, "mq_grouped_swiglu")
+    return h

@@ -1,0 +1,85 @@
+"""W4A16 GEMM. Same call as the reference's ``mini_qwen/kernels/w4a16_gemm.py:194-247``.
+
+# === FROZEN SIGNATURE (the reference's, kept) ===
+# def w4a16_gemm(
+#     x:          [M, K], bf16
+#     qweight:    [K // 8, N], int32 (packed int4, nibble i of qweight[j,n] = weight[8j+i,n])
+#     scales:     [K // group_size, N], bf16
+#     qzeros:     [K // group_size, N // 8], int32 (packed int4 along N)
+#     group_size: int = 128
+# ) -> [M, N], bf16
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _cabi
+
+
+_single_offsets: dict = {}   # (M, device) -> int32 [0, M]; a single linear is a one-expert group
+
+
+def _check_w4(x, qweight, scales, qzeros, group_size, E):
+    assert x.is_cuda and qweight.is_cuda, "w4a16 kernels run on CUDA tensors only"
+    assert x.dtype == torch.bfloat16, "activations must be bfloat16"
+    assert qweight.dtype == torch.int32 and qzeros.dtype == torch.int32 and scales.dtype == torch.bfloat16
+    K = x.shape[-1]
+    N = qweight.shape[-1]
+    assert qweight.shape[-2] * 8 == K, "qweight must be [K // 8, N]"
+    assert K % group_size == 0, f"K={K} must be divisible by group_size={group_size}"
+    assert N % 8 == 0, f"N={N} must be a multiple of 8"
+    assert group_size % 32 == 0, "group_size must be a multiple of 32"
+    G = K // group_size
+    assert tuple(scales.shape[-2:]) == (G, N) and tuple(qzeros.shape[-2:]) == (G, N // 8)
+    return K, N
+
+
+def w4a16_grouped_gemm(x, qweight, scales, qzeros, expert_offsets, group_size: int = 128) -> torch.Tensor:
+    """Rows ``offsets[e]:offsets[e+1]`` of x times the dequantised weight of expert e.
+    qweight [E, K/8, N], scales [E, K/g, N], qzeros [E, K/g, N/8], offsets int32 [E+1]."""
+    E = qweight.shape[0]
+    K, N = _check_w4(x, qweight, scales, qzeros, group_size, E)
+    x = x.contiguous()
+    S = x.shape[0]
+    out = torch.zeros(S, N, dtype=torch.bfloat16, device=x.device)
+    rc = _cabi.load().mq_w4a16_grouped_gemm(_cabi.ptr(x), _cabi.ptr(qweight), _cabi.ptr(scales), _cabi.ptr(qzeros),
+                                            _cabi.ptr(expert_offsets), S, E, N, K, group_size, _cabi.ptr(out),
+                                            _cabi.stream_ptr(x.device))
+    _cabi.check(rc, "mq_w4a16_grouped_gemm")
+    return out
+
+
+def w4a16_grouped_swiglu(x, gate, up, expert_offsets, group_size: int = 128) -> torch.Tensor:
+    """Fused gate/up W4A16 projections + SwiGLU; gate and up are (qweight, scales, qzeros) stacks."""
+    E = gate[0].shape[0]
+    K, N = _check_w4(x, *gate, group_size, E)
+    _check_w4(x, *up, group_size, E)
+    x = x.contiguous()
+    S = x.shape[0]
+    h = torch.zeros(S, N, dtype=torch.bfloat16, device=x.device)
+    rc = _cabi.load().mq_w4a16_grouped_swiglu(_cabi.ptr(x), _cabi.ptr(gate[0]), _cabi.ptr(gate[1]), _cabi.ptr(gate[2]),
+                                              _cabi.ptr(up[0]), _cabi.ptr(up[1]), _cabi.ptr(up[2]),
+                                              _cabi.ptr(expert_offsets), S, E, N, K, group_size, _cabi.ptr(h),
+                                              _cabi.stream_ptr(x.device))
+    _cabi.check(rc, "mq_w4a16_grouped_swiglu")
+    return h
+
+
+def w4a16_gemm(
+    x: torch.Tensor,
+    qweight: torch.Tensor,
+    scales: torch.Tensor,
+    qzeros: torch.Tensor,
+    group_size: int = 128,
+) -> torch.Tensor:
+    """``x @ dequant(qweight)`` with ``W[k,n] = (q[k,n] - z[k//g,n]) * s[k//g,n]``; returns bf16 [M, N]."""
+    assert x.dim() == 2 and qweight.dim() == 2
+    M = x.shape[0]
+    key = (M, x.device)
+    offsets = _single_offsets.get(key)
+    if offsets is None:
+        if len(_single_offsets) > 256:
+            _single_offsets.clear()
+        offsets = _single_offsets[key] = torch.tensor([0, M], dtype=torch.int32, device=x.device)
+    return w4a16_grouped_gemm(x, qweight.contiguous().unsqueeze(0), scales.contiguous().unsqueeze(0),
+                              qzeros.contiguous().unsqueeze(0), offsets, group_size)

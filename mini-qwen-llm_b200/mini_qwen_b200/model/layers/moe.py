@@ -1,0 +1,147 @@
+"""Qwen3 MoE FFN block with the module tree and interface of the reference's
+``mini_qwen/model/layers/moe.py:28-78`` (``gate``, ``experts[e].{gate,up,down}_proj``,
+``forward``, ``quantize_to_w4a16``), executed as a fixed chain of grouped kernels instead of a
+Python loop over experts.
+
+The per-expert modules stay the owners of the weights as far as ``state_dict`` /
+``load_state_dict`` / ``set_submodule`` are concerned.  Before the first forward (or when
+:meth:`finalize` is called) their tensors are gathered once into expert-major stacks and the
+module tensors are re-pointed at views of those stacks, so nothing is stored twice and in-place
+loads keep working.  Replacing an expert projection module, or moving the block to another
+device or dtype, invalidates the stacks; the next forward rebuilds them.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ...kernels.moe_grouped_gemm import moe_grouped_gemm, moe_grouped_swiglu
+from ...kernels.moe_permute import gather_rows, moe_permute_plan
+from ...kernels.moe_router import moe_router
+from ...kernels.moe_unpermute import unpermute_combine
+from ...kernels.w4a16_gemm import w4a16_grouped_gemm, w4a16_grouped_swiglu
+from .linear_w4a16 import LinearW4A16
+
+_PROJ = ("gate_proj", "up_proj", "down_proj")
+
+
+class _ExpertMLP(nn.Module):
+    """SwiGLU MLP of one expert; names match HF ``experts[e].gate_proj / up_proj / down_proj``."""
+
+    def __init__(self, config, epoch: list):
+        super().__init__()
+        object.__setattr__(self, "_epoch", epoch)      # shared counter, not a submodule/buffer
+        self.gate_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=False)
+        self.up_proj = nn.Linear(config.hidden_size, config.intermediate_size, bias=False)
+        self.down_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=False)
+
+    def __setattr__(self, name, value):
+        if name in _PROJ:
+            self._epoch[0] += 1                        # a projection was swapped: stacks are stale
+        super().__setattr__(name, value)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Single-expert path (kept for callers that address one expert; the block does not use it)."""
+        return self.down_proj(nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+class Qwen3MoEBlock(nn.Module):
+    """router -> permute -> grouped gate/up + SwiGLU -> grouped down -> weighted combine."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.num_experts = config.num_experts
+        self.num_experts_per_tok = config.num_experts_per_tok
+        self.norm_topk_prob = getattr(config, "norm_topk_prob", True)
+        self._epoch = [0]
+        self._stacked_epoch = -1
+        self._stacks = None
+        self.gate = nn.Linear(config.hidden_size, config.num_experts, bias=False)
+        self.experts = nn.ModuleList([_ExpertMLP(config, self._epoch) for _ in range(config.num_experts)])
+        self.router_bias = None       # optional fp32 [E] logit bias (not in the reference)
+
+    # ------------------------------------------------------------------ weight stacks
+    def _apply(self, fn, *args, **kwargs):
+        self._epoch[0] += 1           # .to()/.cuda()/.half() re-create the parameter storage
+        return super()._apply(fn, *args, **kwargs)
+
+    def _sentinel(self):
+        first, last = self.experts[0].gate_proj, self.experts[-1].down_proj
+        a = first.qweight if isinstance(first, LinearW4A16) else first.weight
+        b = last.qweight if isinstance(last, LinearW4A16) else last.weight
+        return (a.data_ptr(), b.data_ptr())
+
+    def finalize(self) -> None:
+        """Gather the per-expert tensors into expert-major stacks (idempotent)."""
+        kinds = {isinstance(getattr(ex, p), LinearW4A16) for ex in self.experts for p in _PROJ}
+        if len(kinds) != 1:
+            raise ValueError("experts mix nn.Linear and LinearW4A16 projections; quantise all or none")
+        quantised = kinds.pop()
+        with torch.no_grad():
+            if quantised:
+                stacks = {"w4": True}
+                groups = {getattr(ex, p).group_size for ex in self.experts for p in _PROJ}
+                if len(groups) != 1:
+                    raise ValueError("all expert projections must share one group_size")
+                stacks["group_size"] = groups.pop()
+                for p in _PROJ:
+                    mods = [getattr(ex, p) for ex in self.experts]
+                    trio = []
+                    for buf in ("qweight", "scales", "qzeros"):
+                        st = torch.stack([getattr(m, buf) for m in mods]).contiguous()
+                        for e, m in enumerate(mods):
+                            m._buffers[buf] = st[e]
+                        trio.append(st)
+                    stacks[p] = tuple(trio)
+            else:
+                stacks = {"w4": False}
+                g = [ex.gate_proj.weight for ex in self.experts]
+                u = [ex.up_proj.weight for ex in self.experts]
+                d = [ex.down_proj.weight for ex in self.experts]
+                inter = g[0].shape[0]
+                w13 = torch.cat([torch.stack([w.data for w in g]), torch.stack([w.data for w in u])], dim=1).contiguous()
+                w2 = torch.stack([w.data for w in d]).contiguous()
+                for e, ex in enumerate(self.experts):
+                    ex.gate_proj.weight.data = w13[e, :inter]
+                    ex.up_proj.weight.data = w13[e, inter:]
+                    ex.down_proj.weight.data = w2[e]
+                stacks["w13"], stacks["w2"] = w13, w2
+        self._stacks = stacks
+        self._stacked_epoch = self._epoch[0]
+        self._stacked_sentinel = self._sentinel()
+
+    def _ready(self):
+        if (self._stacks is None or self._stacked_epoch != self._epoch[0]
+                or self._stacked_sentinel != self._sentinel()):
+            self.finalize()
+        return self._stacks
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2d = x.reshape(-1, shape[-1])
+        if not x2d.is_contiguous():
+            x2d = x2d.contiguous()
+        T = x2d.shape[0]
+        K, E = self.num_experts_per_tok, self.num_experts
+        st = self._ready()
+
+        _, weights, ids32 = moe_router(x2d, self.gate.weight, K, bias=self.router_bias,
+                                       renormalize=self.norm_topk_prob, return_int32_ids=True)
+        perm, inv, off32, _ = moe_permute_plan(ids32, E, want_int64_offsets=False)
+        permuted = gather_rows(x2d, perm, K)
+        if st["w4"]:
+            h = w4a16_grouped_swiglu(permuted, st["gate_proj"], st["up_proj"], off32, st["group_size"])
+            out_perm = w4a16_grouped_gemm(h, *st["down_proj"], off32, st["group_size"])
+        else:
+            h = moe_grouped_swiglu(permuted, st["w13"], off32)
+            out_perm = moe_grouped_gemm(h, st["w2"], off32)
+        out = unpermute_combine(out_perm, weights, inv, T, K)
+        return out.reshape(shape)
+
+    def quantize_to_w4a16(self, group_size: int = 128) -> None:
+        """Replace every expert Linear by a min-max quantised ``LinearW4A16`` on the same device."""
+        device = next(self.parameters()).device
+        for expert in self.experts:
+            for p in _PROJ:
+                setattr(expert, p, LinearW4A16.from_float(getattr(expert, p), group_size).to(device))
