@@ -1,0 +1,292 @@
+#!/usr/bin/env python
+"""MoE-layer throughput benchmark.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" = one forward of the Qwen3-30B-A3B-shaped MoE layer (router -> permute -> grouped
+SwiGLU expert GEMM -> combine) over one batch of seeded synthetic tokens.  Default workload:
+bf16 prefill, T=4096 tokens, H=2048, E=128, top-8, I=768.  Prints ONE JSON line on rank 0.
+
+--impl reference times the CPU restatement of the reference's per-expert-loop path (oracle/) on
+the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "mini-qwen-llm_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+H, E, TOPK, I = 2048, 128, 8, 768
+T_PREFILL = 4096
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+CPU_SAMPLE_T = 512
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+        self._period = period_s
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self._period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def build_dense_block(lay, device):
+    from mini_qwen_b200 import Qwen3MoEConfig
+    from mini_qwen_b200.model.layers import Qwen3MoEBlock
+
+    cfg = Qwen3MoEConfig(hidden_size=H, intermediate_size=I, num_experts=E, num_experts_per_tok=TOPK)
+    with torch.device("meta"):
+        blk = Qwen3MoEBlock(cfg)
+    blk = blk.to_empty(device=device).to(torch.bfloat16)
+    sd = {"gate.weight": lay.router}
+    for e in range(E):
+        sd[f"experts.{e}.gate_proj.weight"] = lay.gate[e]
+        sd[f"experts.{e}.up_proj.weight"] = lay.up[e]
+        sd[f"experts.{e}.down_proj.weight"] = lay.down[e]
+    blk.load_state_dict(sd)
+    blk.finalize()
+    return blk
+
+
+def cpu_reference_tokens_per_s(lay, steps, warmup, sample_t):
+    """The reference's per-expert-loop path (CPU restatement) on `sample_t`-token slices of the batch."""
+    from oracle import moe_oracle as O
+
+    torch.set_num_threads(os.cpu_count())
+    T = lay.x.shape[0]
+    times = []
+    for i in range(warmup + steps):
+        lo = (i * sample_t) % max(T - sample_t + 1, 1)
+        x = lay.x[lo:lo + sample_t]
+        t0 = time.perf_counter()
+        O.block_forward(x, lay.router, lay.gate, lay.up, lay.down, lay.top_k, True)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    total = sum(times)
+    return sample_t * len(times) / total, 1e3 * total / len(times)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from mini_qwen_b200 import synthetic
+
+    lay = synthetic.dense_layer(1, T_PREFILL, H, E, TOPK, I, torch.bfloat16)
+    tps, ms = cpu_reference_tokens_per_s(lay, args.steps, args.warmup, CPU_SAMPLE_T)
+    cores = os.cpu_count()
+    sample = f"{CPU_SAMPLE_T}-token slices of the {T_PREFILL}-token batch, one slice per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"bf16 prefill MoE layer T={T_PREFILL} H={H} E={E} top{TOPK} I={I} (seed 1), "
+                               "reference per-expert loop on host cores"},
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    from mini_qwen_b200 import _cabi, synthetic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _cabi.load()
+
+    lay = synthetic.dense_layer(1, T_PREFILL, H, E, TOPK, I, torch.bfloat16)
+    blk = build_dense_block(lay, dev)
+    T = T_PREFILL
+    x_host = lay.x.pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    x_dev = lay.x.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    # ---- device-resident throughput, with per-kernel events on the launching stream
+    with torch.no_grad():
+        for _ in range(args.warmup):
+            blk(x_dev)
+        barrier()
+        blk.kernel_events = []
+        _cabi.launch_count = 0
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            start.record()
+            for _ in range(args.steps):
+                blk(x_dev)
+            end.record()
+            barrier()
+        launches = _cabi.launch_count
+        events, blk.kernel_events = blk.kernel_events, None
+    ms_total = max_over_ranks(start.elapsed_time(end))
+    ms_step = ms_total / args.steps
+    value = world * T * args.steps / (ms_total * 1e-3)
+
+    kern = {}
+    for name, a, b in events:
+        kern.setdefault(name, []).append(a.elapsed_time(b))
+    kern_ms = {k: sum(v) / len(v) for k, v in kern.items()}
+
+    # ---- end to end: pinned host input -> device -> block -> device -> pinned host output, every step
+    with torch.no_grad():
+        for _ in range(max(3, args.warmup // 2)):
+            x_dev.copy_(x_host, non_blocking=True)
+            out_host.copy_(blk(x_dev), non_blocking=True)
+        barrier()
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for _ in range(args.steps):
+            x_dev.copy_(x_host, non_blocking=True)
+            out_host.copy_(blk(x_dev), non_blocking=True)
+        e2.record()
+        barrier()
+    e2e_ms = max_over_ranks(s2.elapsed_time(e2))
+    e2e_value = world * T * args.steps / (e2e_ms * 1e-3)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    S = T * TOPK
+    gemm1_flops = 2.0 * S * (2 * I) * H          # gate+up projections of all slots
+    gemm1_ms = kern_ms.get("grouped_swiglu")
+    roofline = None
+    if gemm1_ms:
+        achieved = gemm1_flops / (gemm1_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "grouped gate/up GEMM + SwiGLU", "achieved": achieved,
+                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                    "peak_source": f"{peaks['source']} burst bf16 GEMM", "traffic": None,
+                    "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms}
+
+    cpu_base = None
+    if world == 1 and not args.no_cpu_baseline:
+        tps, _ = cpu_reference_tokens_per_s(lay, steps=6, warmup=1, sample_t=T_PREFILL // 2)
+        cpu_base = {"value": tps, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                    "sample": f"6 passes over {T_PREFILL // 2}-token halves of the batch after 1 warm-up"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"bf16 prefill MoE layer T={T} per GPU, H={H} E={E} top{TOPK} I={I} (seed 1)",
+                   "l2": "per-step working set 1.2 GB of expert weights > 126 MB L2; no flush needed",
+                   "parallelism": "single GPU" if world == 1 else f"{world} replicas"},
+        "roofline": roofline, "cpu_baseline": cpu_base,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
+                "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches, "clocks": clocks.summary(),
+        "kernels_ms": kern_ms,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
