@@ -35,6 +35,12 @@ PROTOTYPES = {
 }
 
 _lib = None
+launch_count = 0   # kernels launched through this binding (each wrapper adds what it launched)
+
+
+def count_launches(n: int) -> None:
+    global launch_count
+    launch_count += n
 
 
 def lib_path() -> Path:

@@ -18,11 +18,13 @@ def moe_grouped_gemm(
     permuted_hidden: torch.Tensor,   # [num_tokens * top_k, hidden_dim]
     expert_weights: torch.Tensor,    # [num_experts, out_dim, hidden_dim]
     expert_offsets: torch.Tensor,    # [num_experts + 1]
+    status: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """``out[s:t] = permuted_hidden[s:t] @ expert_weights[e].T`` per expert, fp32 accumulation.
 
     Unlike the reference there is no CPU branch (``moe_grouped_gemm.py:124-125``): CPU tensors
-    are an error.  Rows covered by no expert are zero, as in the reference's oracle."""
+    are an error.  Rows covered by no expert are zero, as in the reference's oracle.
+    ``status`` (int32 [1], optional) receives device-side error bits (a bounded wait that ran out)."""
     _cabi.require_cuda(permuted_hidden, expert_weights, expert_offsets)
     assert permuted_hidden.dim() == 2 and expert_weights.dim() == 3
     assert permuted_hidden.dtype == expert_weights.dtype, "activations and weights must share a dtype"
@@ -32,11 +34,13 @@ def moe_grouped_gemm(
     w = expert_weights.contiguous()
     S = a.shape[0]
     out = torch.zeros(S, D, dtype=a.dtype, device=a.device)
-    status = _status_word(a.device)
+    if status is None:
+        status = _status_word(a.device)
     rc = _cabi.load().mq_grouped_gemm(_cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(_offsets32(expert_offsets)), S, E, D, H,
                                       _cabi.dtype_code(a), _cabi.ptr(out), _cabi.ptr(status),
                                       _cabi.stream_ptr(a.device))
     _cabi.check(rc, "mq_grouped_gemm")
+    _cabi.count_launches(1 if S else 0)
     return out
 
 
@@ -57,4 +61,5 @@ def moe_grouped_swiglu(permuted_hidden: torch.Tensor, gate_up_weights: torch.Ten
                                         S, E, I2 // 2, H, _cabi.dtype_code(a), _cabi.ptr(h), _cabi.ptr(status),
                                         _cabi.stream_ptr(a.device))
     _cabi.check(rc, "mq_grouped_swiglu")
+    _cabi.count_launches(1 if S else 0)
     return h

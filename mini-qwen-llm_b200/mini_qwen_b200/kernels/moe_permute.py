@@ -32,6 +32,7 @@ def moe_permute_plan(topk_ids: torch.Tensor, num_experts: int, want_int64_offset
                              _cabi.ptr(inv), _cabi.ptr(off64), _cabi.ptr(off32), _cabi.ptr(ws), ws_bytes,
                              _cabi.stream_ptr(dev))
     _cabi.check(rc, "mq_permute_plan")
+    _cabi.count_launches(1 if S <= 2048 else 3)
     return perm, inv, off32, off64
 
 
@@ -43,6 +44,7 @@ def gather_rows(hidden_states: torch.Tensor, perm: torch.Tensor, top_k: int) -> 
     rc = _cabi.load().mq_gather_rows(_cabi.ptr(x), _cabi.dtype_code(x), _cabi.ptr(perm), S, top_k, H,
                                      _cabi.ptr(out), _cabi.stream_ptr(x.device))
     _cabi.check(rc, "mq_gather_rows")
+    _cabi.count_launches(1 if S else 0)
     return out
 
 

@@ -45,4 +45,5 @@ def moe_router(
                             T, H, E, top_k, int(renormalize), _cabi.ptr(logits), _cabi.ptr(ids), _cabi.ptr(ids32),
                             _cabi.ptr(wts), _cabi.stream_ptr(dev))
     _cabi.check(rc, "mq_router_topk")
+    _cabi.count_launches(2 if T else 0)
     return (ids, wts, ids32) if return_int32_ids else (ids, wts)

@@ -19,6 +19,7 @@ def unpermute_combine(permuted_output: torch.Tensor, topk_weights: torch.Tensor,
     rc = _cabi.load().mq_unpermute_combine(_cabi.ptr(rows), _cabi.dtype_code(rows), _cabi.ptr(w), _cabi.ptr(inv),
                                            num_tokens, top_k, H, _cabi.ptr(out), _cabi.stream_ptr(rows.device))
     _cabi.check(rc, "mq_unpermute_combine")
+    _cabi.count_launches(1 if num_tokens else 0)
     return out
 
 

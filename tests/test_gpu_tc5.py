@@ -1,0 +1,75 @@
+"""GPU parity of the tcgen05/TMEM grouped GEMM (bf16, N % 128 == 0, K % 64 == 0) against the CPU
+oracle, from a single tile up to the benchmark shapes; the device status word must stay 0."""
+import pytest
+import torch
+
+from mini_qwen_b200.kernels import moe_grouped_gemm, moe_grouped_swiglu
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def offsets_from_counts(counts):
+    off = torch.zeros(len(counts) + 1, dtype=torch.int64)
+    off[1:] = torch.cumsum(torch.tensor(counts), 0)
+    return off
+
+
+CASES = [
+    ([128], 128, 64),                 # one tile, one k block
+    ([128], 256, 256),                # one tile, 4 k blocks (one trip round the ring)
+    ([100], 128, 512),                # partial tile, ring wraps
+    ([130, 0, 5, 300], 256, 192),     # tiles straddling expert ends, an empty expert
+    ([1, 1, 1, 1, 1, 1, 1, 1], 512, 128),
+    ([257] * 16, 2048, 768),          # down-projection shape
+    ([700, 13, 0, 0, 1500, 128, 127, 129], 768, 2048),
+]
+
+
+@pytest.mark.parametrize("counts,N,Kd", CASES)
+def test_tc5_grouped_gemm(counts, N, Kd):
+    E, S = len(counts), sum(counts)
+    g = torch.Generator().manual_seed(S + N + Kd)
+    a = torch.randn(S, Kd, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, N, Kd, generator=g) * 0.05).to(torch.bfloat16)
+    off = offsets_from_counts(counts)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = moe_grouped_gemm(a.to(DEV), w.to(DEV), off.to(DEV), status=status)
+    assert status.item() == 0, "a bounded wait ran out inside the kernel"
+    ref = O.grouped_gemm(a, w, off)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-3)
+    # fp32 accumulation of exact bf16 products: only rounding-boundary flips may differ
+    assert (out.cpu() != ref).float().mean() < 0.01
+
+
+@pytest.mark.parametrize("counts,I,H", [([128], 128, 64), ([90, 0, 200], 256, 256), ([300] * 8, 768, 2048)])
+def test_tc5_grouped_swiglu(counts, I, H):
+    E, S = len(counts), sum(counts)
+    g = torch.Generator().manual_seed(S + I + H)
+    a = torch.randn(S, H, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(E, I, H, generator=g) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(E, I, H, generator=g) * 0.05).to(torch.bfloat16)
+    off = offsets_from_counts(counts)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    h = moe_grouped_swiglu(a.to(DEV), torch.cat([wg, wu], 1).to(DEV), off.to(torch.int32).to(DEV), status=status)
+    assert status.item() == 0
+    ref = torch.zeros(S, I, dtype=torch.bfloat16)
+    for e in range(E):
+        s, t = int(off[e]), int(off[e + 1])
+        if t > s:
+            ref[s:t] = torch.nn.functional.silu(a[s:t] @ wg[e].T) * (a[s:t] @ wu[e].T)
+    torch.testing.assert_close(h.cpu().float(), ref.float(), rtol=2e-2, atol=2e-3)
+
+
+def test_tc5_rows_outside_experts_untouched():
+    # offsets that do not start at 0 / end at S: rows outside stay zero
+    a = torch.randn(300, 64, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    w = torch.randn(2, 128, 64, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    off = torch.tensor([10, 150, 280])
+    out = moe_grouped_gemm(a.to(DEV), w.to(DEV), off.to(DEV)).cpu()
+    assert float(out[:10].abs().max()) == 0 and float(out[280:].abs().max()) == 0
+    ref = torch.zeros(300, 128, dtype=torch.bfloat16)
+    ref[10:150] = (a[10:150].float() @ w[0].float().T).to(torch.bfloat16)
+    ref[150:280] = (a[150:280].float() @ w[1].float().T).to(torch.bfloat16)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-3)
