@@ -105,16 +105,8 @@ def build_dense_block(lay, device):
     from mini_qwen_b200.model.layers import Qwen3MoEBlock
 
     cfg = Qwen3MoEConfig(hidden_size=H, intermediate_size=I, num_experts=E, num_experts_per_tok=TOPK)
-    with torch.device("meta"):
-        blk = Qwen3MoEBlock(cfg)
-    blk = blk.to_empty(device=device).to(torch.bfloat16)
-    sd = {"gate.weight": lay.router}
-    for e in range(E):
-        sd[f"experts.{e}.gate_proj.weight"] = lay.gate[e]
-        sd[f"experts.{e}.up_proj.weight"] = lay.up[e]
-        sd[f"experts.{e}.down_proj.weight"] = lay.down[e]
-    blk.load_state_dict(sd)
-    blk.finalize()
+    w13 = torch.cat([lay.gate, lay.up], dim=1).to(device)
+    blk = Qwen3MoEBlock.from_stacked(cfg, lay.router.to(device), w13, lay.down.to(device))
     return blk
 
 

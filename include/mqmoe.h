@@ -53,15 +53,17 @@ const char* mq_last_cuda_error(void);
  * scores are ordered by ascending expert id.  renormalize != 0 additionally divides the K
  * weights by their sum (mini_qwen/model/layers/moe.py:55-56).
  *   x [T,H] (x_dtype), w [E,H] (w_dtype), bias fp32 [E] or NULL,
- *   logits_ws fp32 [T,E] caller-provided workspace (overwritten),
+ *   logits_ws: caller-provided workspace of mq_router_workspace_bytes(T, H, E) bytes (overwritten;
+ *   holds the fp32 logits, in several K slices when the batch alone would not fill the GPU),
  *   ids64 int64 [T,K] and/or ids32 int32 [T,K] (either may be NULL, not both),
  *   weights fp32 [T,K].
  * Limits: 1 <= K <= E <= 1024, K <= 32.
  */
+size_t mq_router_workspace_bytes(int64_t T, int64_t H, int64_t E);
 int mq_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
                    int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
-                   float* logits_ws, int64_t* ids64, int32_t* ids32, float* weights,
-                   void* stream);
+                   float* logits_ws, size_t logits_ws_bytes, int64_t* ids64, int32_t* ids32,
+                   float* weights, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Permute plan.  Replaces the index work of moe_permute / moe_unpermute
@@ -99,7 +101,7 @@ int mq_unpermute_combine(const void* rows, int dtype, const float* weights, cons
  * out[off[e]:off[e+1], :] = a[off[e]:off[e+1], :] . w[e]^T with fp32 accumulation.
  *   a [S,Kd], w [E,N,Kd], out [S,N], all of type `dtype`; offsets int32 [E+1].
  * Rows of `out` that belong to no expert are not written.
- * bf16 with Kd % 64 == 0 and N % 64 == 0 runs on the tcgen05/TMEM kernel, everything else on
+ * bf16 with Kd % 64 == 0 and N % 128 == 0 runs on the tcgen05/TMEM kernel, everything else on
  * a generic tiled kernel (Kd % 8 == 0 for 16-bit types, % 4 for fp32).
  */
 int mq_grouped_gemm(const void* a, const void* w, const int32_t* offsets,

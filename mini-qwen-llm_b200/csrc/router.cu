@@ -47,82 +47,85 @@ __device__ __forceinline__ void load8_safe(const void* p, int dt, size_t row_bas
 }
 
 // ---------------------------------------------------------------------------------------------
-// Tiled logits: CTA = 32 tokens x 64 experts, 128 threads, each thread 4 tokens x 4 experts.
-constexpr int R_TM = 32, R_TE = 64, R_KC = 32, R_THREADS = 128;
+// Tiled logits: CTA = 32 tokens x 128 experts x one K slice, 128 threads, each thread 4 tokens x 8
+// experts.  The K dimension is split over blockIdx.z so that small batches still fill the GPU; the
+// slices are summed in a fixed order by the selection kernel, so results do not depend on timing.
+constexpr int R_TM = 32, R_TE = 128, R_KC = 32, R_THREADS = 128;
 
 __global__ void __launch_bounds__(R_THREADS)
 router_logits_tiled(const void* __restrict__ x, int xdt, const void* __restrict__ w, int wdt,
-                    int64_t T, int64_t H, int64_t E, int vec_ok, float* __restrict__ logits) {
+                    int64_t T, int64_t H, int64_t E, int64_t k_per_slice, int vec_ok,
+                    float* __restrict__ logits /* [slices, T, E] */) {
   __shared__ __align__(16) float xs[R_KC][R_TM];
   __shared__ __align__(16) float ws[R_KC][R_TE];
 
   const int tid = threadIdx.x;
   const int64_t t0 = (int64_t)blockIdx.x * R_TM;
   const int64_t e0 = (int64_t)blockIdx.y * R_TE;
+  const int64_t k_lo = (int64_t)blockIdx.z * k_per_slice;
+  const int64_t k_hi = min(k_lo + k_per_slice, H);
   const int tg = tid >> 4, eg = tid & 15;
 
-  // loader roles: x tile: token tid%32, k part tid/32 (8 wide); w tile: expert tid%64, k part tid/64 (16 wide)
+  // loader roles: x tile: token tid%32, k part tid/32 (8 wide); w tile: expert tid, all 32 k
   const int lx_tok = tid & 31, lx_k = (tid >> 5) * 8;
-  const int lw_e = tid & 63, lw_k = (tid >> 6) * 16;
   const bool x_in = t0 + lx_tok < T;
-  const bool w_in = e0 + lw_e < E;
+  const bool w_in = e0 + tid < E;
   const size_t x_row = (size_t)(t0 + lx_tok) * H;
-  const size_t w_row = (size_t)(e0 + lw_e) * H;
+  const size_t w_row = (size_t)(e0 + tid) * H;
 
-  float acc[4][4];
+  float acc[4][8];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
 
-  float px[8], pw0[8], pw1[8];
+  float px[8], pw[4][8];
   auto fetch = [&](int64_t k0) {
-    if (x_in) load8_safe(x, xdt, x_row, k0 + lx_k, H, vec_ok, px);
-    else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) px[j] = 0.0f;
-    }
-    if (w_in) {
-      load8_safe(w, wdt, w_row, k0 + lw_k, H, vec_ok, pw0);
-      load8_safe(w, wdt, w_row, k0 + lw_k + 8, H, vec_ok, pw1);
-    } else {
+    for (int j = 0; j < 8; ++j) px[j] = 0.0f;
+    if (x_in && k0 + lx_k < k_hi) load8_safe(x, xdt, x_row, k0 + lx_k, k_hi, vec_ok, px);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { pw0[j] = 0.0f; pw1[j] = 0.0f; }
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) pw[q][j] = 0.0f;
+      if (w_in && k0 + 8 * q < k_hi) load8_safe(w, wdt, w_row, k0 + 8 * q, k_hi, vec_ok, pw[q]);
     }
   };
 
-  fetch(0);
-  for (int64_t k0 = 0; k0 < H; k0 += R_KC) {
+  fetch(k_lo);
+  for (int64_t k0 = k_lo; k0 < k_hi; k0 += R_KC) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      xs[lx_k + j][lx_tok] = px[j];
-      ws[lw_k + j][lw_e] = pw0[j];
-      ws[lw_k + 8 + j][lw_e] = pw1[j];
-    }
+    for (int j = 0; j < 8; ++j) xs[lx_k + j][lx_tok] = px[j];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ws[8 * q + j][tid] = pw[q][j];
     __syncthreads();
-    if (k0 + R_KC < H) fetch(k0 + R_KC);
+    if (k0 + R_KC < k_hi) fetch(k0 + R_KC);
 #pragma unroll
     for (int k = 0; k < R_KC; ++k) {
-      float4 xv = *reinterpret_cast<const float4*>(&xs[k][4 * tg]);
-      float4 wv = *reinterpret_cast<const float4*>(&ws[k][4 * eg]);
+      const float4 xv = *reinterpret_cast<const float4*>(&xs[k][4 * tg]);
+      const float4 wa = *reinterpret_cast<const float4*>(&ws[k][4 * eg]);
+      const float4 wb = *reinterpret_cast<const float4*>(&ws[k][64 + 4 * eg]);
       const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
-      const float wa[4] = {wv.x, wv.y, wv.z, wv.w};
+      const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wa[j], acc[i][j]);
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(xa[i], wv[j], acc[i][j]);
     }
     __syncthreads();
   }
 
+  float* dst = logits + (size_t)blockIdx.z * T * E;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    int64_t t = t0 + 4 * tg + i;
+    const int64_t t = t0 + 4 * tg + i;
     if (t >= T) continue;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      int64_t e = e0 + 4 * eg + j;
-      if (e < E) logits[t * E + e] = acc[i][j];
+    for (int j = 0; j < 8; ++j) {
+      const int64_t e = e0 + (j < 4 ? 4 * eg + j : 64 + 4 * eg + (j - 4));
+      if (e < E) dst[t * E + e] = acc[i][j];
     }
   }
 }
@@ -167,7 +170,7 @@ router_logits_skinny(const void* __restrict__ x, int xdt, const void* __restrict
 // One warp per token: softmax over E logits, then K rounds of warp arg-max on (score, -id).
 template <int EPL>
 __global__ void __launch_bounds__(128)
-router_softmax_topk(const float* __restrict__ logits, const float* __restrict__ bias,
+router_softmax_topk(const float* __restrict__ logits, int slices, const float* __restrict__ bias,
                     int64_t T, int E, int K, int renorm,
                     int64_t* __restrict__ ids64, int32_t* __restrict__ ids32, float* __restrict__ weights) {
   const int lane = threadIdx.x & 31;
@@ -182,6 +185,7 @@ router_softmax_topk(const float* __restrict__ logits, const float* __restrict__ 
     float v = -INFINITY;
     if (e < E) {
       v = logits[t * E + e];
+      for (int sl = 1; sl < slices; ++sl) v += logits[((size_t)sl * T + t) * E + e];   // fixed order
       if (bias != nullptr) v += bias[e];
     }
     s[j] = v;
@@ -233,45 +237,70 @@ router_softmax_topk(const float* __restrict__ logits, const float* __restrict__ 
 }
 
 template <int EPL>
-void launch_topk(const float* logits, const float* bias, int64_t T, int E, int K, int renorm,
+void launch_topk(const float* logits, int slices, const float* bias, int64_t T, int E, int K, int renorm,
                  int64_t* ids64, int32_t* ids32, float* weights, cudaStream_t st) {
   unsigned blocks = (unsigned)((T + 3) / 4);
-  router_softmax_topk<EPL><<<blocks, 128, 0, st>>>(logits, bias, T, E, K, renorm, ids64, ids32, weights);
+  router_softmax_topk<EPL><<<blocks, 128, 0, st>>>(logits, slices, bias, T, E, K, renorm, ids64, ids32, weights);
 }
 
 }  // namespace
 }  // namespace mq
 
+namespace mq {
+namespace {
+// K slices for the tiled logits kernel: enough CTAs for two per SM, slices a multiple of 32 wide.
+int router_slices(int64_t T, int64_t H, int64_t E) {
+  if (T <= 64) return 1;
+  const int64_t ctas = ((T + R_TM - 1) / R_TM) * ((E + R_TE - 1) / R_TE);
+  int64_t s = (2 * 148 + ctas - 1) / ctas;
+  const int64_t max_s = (H + 255) / 256;          // keep at least 256 k per slice
+  if (s > max_s) s = max_s;
+  if (s > 8) s = 8;
+  if (s < 1) s = 1;
+  return (int)s;
+}
+}  // namespace
+}  // namespace mq
+
+extern "C" size_t mq_router_workspace_bytes(int64_t T, int64_t H, int64_t E) {
+  if (T <= 0 || E <= 0 || H <= 0) return 16;
+  return (size_t)mq::router_slices(T, H, E) * (size_t)T * (size_t)E * sizeof(float);
+}
+
 extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
                               int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
-                              float* logits_ws, int64_t* ids64, int32_t* ids32, float* weights,
-                              void* stream) {
+                              float* logits_ws, size_t logits_ws_bytes, int64_t* ids64, int32_t* ids32,
+                              float* weights, void* stream) {
   using namespace mq;
   if (T < 0 || H <= 0 || E <= 0 || K <= 0) return MQ_ERR_INVALID_ARGUMENT;
   if (!valid_dtype(x_dtype) || !valid_dtype(w_dtype)) return MQ_ERR_INVALID_ARGUMENT;
   if (K > E || E > 1024 || K > 32) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (T == 0) return MQ_OK;
   if (!x || !w || !logits_ws || !weights || (!ids64 && !ids32)) return MQ_ERR_INVALID_ARGUMENT;
+  if (logits_ws_bytes < mq_router_workspace_bytes(T, H, E)) return MQ_ERR_WORKSPACE_TOO_SMALL;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
   // vector loads need 16-byte rows: H a multiple of 8 elements and aligned bases
   int vec_ok = (H % 8 == 0) && aligned16(x) && aligned16(w);
 
+  int slices = 1;
   if (T <= 64) {
     router_logits_skinny<<<(unsigned)E, 128, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, vec_ok, logits_ws);
   } else {
-    dim3 grid((unsigned)((T + R_TM - 1) / R_TM), (unsigned)((E + R_TE - 1) / R_TE));
-    router_logits_tiled<<<grid, R_THREADS, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, vec_ok, logits_ws);
+    slices = router_slices(T, H, E);
+    int64_t k_per_slice = ((H + slices - 1) / slices + R_KC - 1) / R_KC * R_KC;
+    dim3 grid((unsigned)((T + R_TM - 1) / R_TM), (unsigned)((E + R_TE - 1) / R_TE), (unsigned)slices);
+    router_logits_tiled<<<grid, R_THREADS, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, k_per_slice, vec_ok, logits_ws);
   }
   int rc = check_launch();
   if (rc != MQ_OK) return rc;
 
   int e = (int)E, k = (int)K;
-  if (E <= 32) launch_topk<1>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
-  else if (E <= 64) launch_topk<2>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
-  else if (E <= 128) launch_topk<4>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
-  else if (E <= 256) launch_topk<8>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
-  else if (E <= 512) launch_topk<16>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
-  else launch_topk<32>(logits_ws, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  if (E <= 32) launch_topk<1>(logits_ws, slices, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else if (E <= 64) launch_topk<2>(logits_ws, slices, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else if (E <= 128) launch_topk<4>(logits_ws, slices, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else if (E <= 256) launch_topk<8>(logits_ws, slices, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else if (E <= 512) launch_topk<16>(logits_ws, slices, bias, T, e, k, renormalize, ids64, ids32, weights, st);
+  else launch_topk<32>(logits_ws, slices, bias, T, e, k, renormalize, ids64, ids32, weights, st);
   return check_launch();
 }

@@ -23,7 +23,8 @@ PROTOTYPES = {
     "mq_version": (c_int, []),
     "mq_status_string": (c_char_p, [c_int]),
     "mq_last_cuda_error": (c_char_p, []),
-    "mq_router_topk": (c_int, [_P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _P, _P, _P]),
+    "mq_router_workspace_bytes": (c_size_t, [_L, _L, _L]),
+    "mq_router_topk": (c_int, [_P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, c_size_t, _P, _P, _P, _P]),
     "mq_permute_workspace_bytes": (c_size_t, [_L, _L]),
     "mq_permute_plan": (c_int, [_P, _I, _L, _L, _L, _P, _P, _P, _P, _P, c_size_t, _P]),
     "mq_gather_rows": (c_int, [_P, _I, _P, _L, _L, _L, _P, _P]),

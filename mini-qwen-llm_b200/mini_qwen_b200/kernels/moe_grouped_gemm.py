@@ -19,12 +19,14 @@ def moe_grouped_gemm(
     expert_weights: torch.Tensor,    # [num_experts, out_dim, hidden_dim]
     expert_offsets: torch.Tensor,    # [num_experts + 1]
     status: torch.Tensor | None = None,
+    zero_init: bool = True,
 ) -> torch.Tensor:
     """``out[s:t] = permuted_hidden[s:t] @ expert_weights[e].T`` per expert, fp32 accumulation.
 
     Unlike the reference there is no CPU branch (``moe_grouped_gemm.py:124-125``): CPU tensors
     are an error.  Rows covered by no expert are zero, as in the reference's oracle.
-    ``status`` (int32 [1], optional) receives device-side error bits (a bounded wait that ran out)."""
+    ``status`` (int32 [1], optional) receives device-side error bits (a bounded wait that ran out).
+    ``zero_init=False`` skips the zero fill when the offsets are known to cover every row."""
     _cabi.require_cuda(permuted_hidden, expert_weights, expert_offsets)
     assert permuted_hidden.dim() == 2 and expert_weights.dim() == 3
     assert permuted_hidden.dtype == expert_weights.dtype, "activations and weights must share a dtype"
@@ -33,7 +35,7 @@ def moe_grouped_gemm(
     a = permuted_hidden.contiguous()
     w = expert_weights.contiguous()
     S = a.shape[0]
-    out = torch.zeros(S, D, dtype=a.dtype, device=a.device)
+    out = (torch.zeros if zero_init else torch.empty)(S, D, dtype=a.dtype, device=a.device)
     if status is None:
         status = _status_word(a.device)
     rc = _cabi.load().mq_grouped_gemm(_cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(_offsets32(expert_offsets)), S, E, D, H,
@@ -45,7 +47,8 @@ def moe_grouped_gemm(
 
 
 def moe_grouped_swiglu(permuted_hidden: torch.Tensor, gate_up_weights: torch.Tensor,
-                       expert_offsets: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor:
+                       expert_offsets: torch.Tensor, status: torch.Tensor | None = None,
+                       zero_init: bool = True) -> torch.Tensor:
     """``h[s:t] = silu(x @ Wg[e].T) * (x @ Wu[e].T)`` with a rounding to the tensor dtype after
     every op, as the per-expert module path rounds.  ``gate_up_weights`` is [E, 2I, H]: gate
     rows first, then up rows."""
@@ -54,7 +57,7 @@ def moe_grouped_swiglu(permuted_hidden: torch.Tensor, gate_up_weights: torch.Ten
     assert I2 % 2 == 0 and permuted_hidden.shape[1] == H
     a = permuted_hidden.contiguous()
     S = a.shape[0]
-    h = torch.zeros(S, I2 // 2, dtype=a.dtype, device=a.device)
+    h = (torch.zeros if zero_init else torch.empty)(S, I2 // 2, dtype=a.dtype, device=a.device)
     if status is None:
         status = _status_word(a.device)
     rc = _cabi.load().mq_grouped_swiglu(_cabi.ptr(a), _cabi.ptr(gate_up_weights), _cabi.ptr(_offsets32(expert_offsets)),

@@ -39,10 +39,11 @@ def moe_router(
     ids = torch.empty(T, top_k, dtype=torch.int64, device=dev)
     ids32 = torch.empty(T, top_k, dtype=torch.int32, device=dev) if return_int32_ids else None
     wts = torch.empty(T, top_k, dtype=torch.float32, device=dev)
-    logits = torch.empty(T, E, dtype=torch.float32, device=dev)
     lib = _cabi.load()
+    ws_bytes = lib.mq_router_workspace_bytes(T, H, E)
+    logits = torch.empty(ws_bytes // 4, dtype=torch.float32, device=dev)
     rc = lib.mq_router_topk(_cabi.ptr(x), _cabi.dtype_code(x), _cabi.ptr(w), _cabi.dtype_code(w), _cabi.ptr(bias),
-                            T, H, E, top_k, int(renormalize), _cabi.ptr(logits), _cabi.ptr(ids), _cabi.ptr(ids32),
+                            T, H, E, top_k, int(renormalize), _cabi.ptr(logits), ws_bytes, _cabi.ptr(ids), _cabi.ptr(ids32),
                             _cabi.ptr(wts), _cabi.stream_ptr(dev))
     _cabi.check(rc, "mq_router_topk")
     _cabi.count_launches(2 if T else 0)

@@ -34,14 +34,15 @@ def _check_w4(x, qweight, scales, qzeros, group_size, E):
     return K, N
 
 
-def w4a16_grouped_gemm(x, qweight, scales, qzeros, expert_offsets, group_size: int = 128) -> torch.Tensor:
+def w4a16_grouped_gemm(x, qweight, scales, qzeros, expert_offsets, group_size: int = 128,
+                       zero_init: bool = True) -> torch.Tensor:
     """Rows ``offsets[e]:offsets[e+1]`` of x times the dequantised weight of expert e.
     qweight [E, K/8, N], scales [E, K/g, N], qzeros [E, K/g, N/8], offsets int32 [E+1]."""
     E = qweight.shape[0]
     K, N = _check_w4(x, qweight, scales, qzeros, group_size, E)
     x = x.contiguous()
     S = x.shape[0]
-    out = torch.zeros(S, N, dtype=torch.bfloat16, device=x.device)
+    out = (torch.zeros if zero_init else torch.empty)(S, N, dtype=torch.bfloat16, device=x.device)
     rc = _cabi.load().mq_w4a16_grouped_gemm(_cabi.ptr(x), _cabi.ptr(qweight), _cabi.ptr(scales), _cabi.ptr(qzeros),
                                             _cabi.ptr(expert_offsets), S, E, N, K, group_size, _cabi.ptr(out),
                                             _cabi.stream_ptr(x.device))
@@ -50,14 +51,14 @@ def w4a16_grouped_gemm(x, qweight, scales, qzeros, expert_offsets, group_size: i
     return out
 
 
-def w4a16_grouped_swiglu(x, gate, up, expert_offsets, group_size: int = 128) -> torch.Tensor:
+def w4a16_grouped_swiglu(x, gate, up, expert_offsets, group_size: int = 128, zero_init: bool = True) -> torch.Tensor:
     """Fused gate/up W4A16 projections + SwiGLU; gate and up are (qweight, scales, qzeros) stacks."""
     E = gate[0].shape[0]
     K, N = _check_w4(x, *gate, group_size, E)
     _check_w4(x, *up, group_size, E)
     x = x.contiguous()
     S = x.shape[0]
-    h = torch.zeros(S, N, dtype=torch.bfloat16, device=x.device)
+    h = (torch.zeros if zero_init else torch.empty)(S, N, dtype=torch.bfloat16, device=x.device)
     rc = _cabi.load().mq_w4a16_grouped_swiglu(_cabi.ptr(x), _cabi.ptr(gate[0]), _cabi.ptr(gate[1]), _cabi.ptr(gate[2]),
                                               _cabi.ptr(up[0]), _cabi.ptr(up[1]), _cabi.ptr(up[2]),
                                               _cabi.ptr(expert_offsets), S, E, N, K, group_size, _cabi.ptr(h),
@@ -84,4 +85,4 @@ def w4a16_gemm(
             _single_offsets.clear()
         offsets = _single_offsets[key] = torch.tensor([0, M], dtype=torch.int32, device=x.device)
     return w4a16_grouped_gemm(x, qweight.contiguous().unsqueeze(0), scales.contiguous().unsqueeze(0),
-                              qzeros.contiguous().unsqueeze(0), offsets, group_size)
+                              qzeros.contiguous().unsqueeze(0), offsets, group_size, zero_init=False)

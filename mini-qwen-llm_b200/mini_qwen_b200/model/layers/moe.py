@@ -111,6 +111,30 @@ class Qwen3MoEBlock(nn.Module):
         self._stacked_epoch = self._epoch[0]
         self._stacked_sentinel = self._sentinel()
 
+    @classmethod
+    def from_stacked(cls, config, router_weight: torch.Tensor, gate_up_proj: torch.Tensor,
+                     down_proj: torch.Tensor) -> "Qwen3MoEBlock":
+        """Builds a dense block from expert-major tensors without copying them:
+        ``router_weight`` [E, H], ``gate_up_proj`` [E, 2I, H] (gate rows, then up rows: the fused
+        layout of HF Qwen3-MoE checkpoints), ``down_proj`` [E, H, I].  The per-expert modules become
+        views of the given tensors."""
+        E, I2, H = gate_up_proj.shape
+        assert E == config.num_experts and I2 == 2 * config.intermediate_size and H == config.hidden_size
+        assert tuple(down_proj.shape) == (E, H, I2 // 2) and tuple(router_weight.shape) == (E, H)
+        with torch.device("meta"):
+            blk = cls(config)
+        w13, w2 = gate_up_proj.contiguous(), down_proj.contiguous()
+        blk.gate.weight = nn.Parameter(router_weight, requires_grad=False)
+        inter = I2 // 2
+        for e, ex in enumerate(blk.experts):
+            ex.gate_proj.weight = nn.Parameter(w13[e, :inter], requires_grad=False)
+            ex.up_proj.weight = nn.Parameter(w13[e, inter:], requires_grad=False)
+            ex.down_proj.weight = nn.Parameter(w2[e], requires_grad=False)
+        blk._stacks = {"w4": False, "w13": w13, "w2": w2}
+        blk._stacked_epoch = blk._epoch[0]
+        blk._stacked_sentinel = blk._sentinel()
+        return blk
+
     def _ready(self):
         if (self._stacks is None or self._stacked_epoch != self._epoch[0]
                 or self._stacked_sentinel != self._sentinel()):
@@ -133,12 +157,14 @@ class Qwen3MoEBlock(nn.Module):
         perm, inv, off32, _ = run("permute_plan", moe_permute_plan, ids32, E, want_int64_offsets=False)
         permuted = run("gather_rows", gather_rows, x2d, perm, K)
         if st["w4"]:
+            # the offsets of a routing cover every slot, so no output needs a zero fill
             h = run("grouped_swiglu", w4a16_grouped_swiglu, permuted, st["gate_proj"], st["up_proj"], off32,
-                    st["group_size"])
-            out_perm = run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off32, st["group_size"])
+                    st["group_size"], zero_init=False)
+            out_perm = run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off32, st["group_size"],
+                           zero_init=False)
         else:
-            h = run("grouped_swiglu", moe_grouped_swiglu, permuted, st["w13"], off32)
-            out_perm = run("grouped_down", moe_grouped_gemm, h, st["w2"], off32)
+            h = run("grouped_swiglu", moe_grouped_swiglu, permuted, st["w13"], off32, zero_init=False)
+            out_perm = run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False)
         out = run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K)
         return out.reshape(shape)
 

@@ -145,11 +145,20 @@ def test_cpu_tensors_are_rejected():
 def test_argument_checks_return_status_without_a_gpu():
     lib = _cabi.load()
     # nothing is launched when the argument check fails, so these are safe on a CPU-only host
-    assert lib.mq_router_topk(None, 0, None, 0, None, 4, 32, 8, 9, 0, None, None, None, None, None) == 2   # K > E
-    assert lib.mq_router_topk(None, 0, None, 0, None, 4, 32, 8, 2, 0, None, None, None, None, None) == 1   # null
-    assert lib.mq_router_topk(None, 7, None, 0, None, 4, 32, 8, 2, 0, None, None, None, None, None) == 1   # dtype
+    assert lib.mq_router_topk(None, 0, None, 0, None, 4, 32, 8, 9, 0, None, 0, None, None, None, None) == 2   # K > E
+    assert lib.mq_router_topk(None, 0, None, 0, None, 4, 32, 8, 2, 0, None, 0, None, None, None, None) == 1   # null
+    assert lib.mq_router_topk(None, 7, None, 0, None, 4, 32, 8, 2, 0, None, 0, None, None, None, None) == 1   # dtype
     assert lib.mq_permute_plan(None, 1, 4, 2, 128, None, None, None, None, None, 0, None) == 1             # no offsets
     assert lib.mq_permute_plan(None, 1, 4, 2, 2048, None, None, None, None, None, 0, None) == 2            # E > 1024
     assert lib.mq_w4a16_grouped_gemm(None, None, None, None, None, 4, 1, 8, 128, 48, None, None) == 2      # group % 32
     assert lib.mq_unpermute_combine(None, 1, None, None, 4, 33, 64, None, None) == 2                        # K > 32
     assert lib.mq_permute_workspace_bytes(131072, 128) >= 64 * 128 * 4
+
+
+def test_from_stacked_shares_storage():
+    cfg = Qwen3MoEConfig(hidden_size=32, intermediate_size=16, num_experts=4, num_experts_per_tok=2)
+    w13, w2, r = torch.randn(4, 32, 32), torch.randn(4, 32, 16), torch.randn(4, 32)
+    blk = Qwen3MoEBlock.from_stacked(cfg, r, w13, w2)
+    assert blk.experts[2].up_proj.weight.data_ptr() == w13[2, 16:].data_ptr()
+    assert torch.equal(blk.state_dict()["experts.3.down_proj.weight"], w2[3])
+    assert blk._ready()["w13"].data_ptr() == w13.data_ptr()       # no restack needed
