@@ -36,7 +36,8 @@ typedef enum {
   MQ_ERR_UNSUPPORTED_SHAPE = 2,  /* a size outside what the kernels cover (see each call) */
   MQ_ERR_WORKSPACE_TOO_SMALL = 3,
   MQ_ERR_LAUNCH_FAILED = 4,      /* cudaGetLastError() after the launch was not cudaSuccess */
-  MQ_ERR_DRIVER_ENTRY = 5        /* cuTensorMapEncodeTiled could not be resolved or failed */
+  MQ_ERR_DRIVER_ENTRY = 5,       /* cuTensorMapEncodeTiled could not be resolved or failed */
+  MQ_ERR_STATIC_SCRATCH_EXCEEDED = 6 /* the request needs more scratch than the library's built-in array */
 } mq_status;
 
 /* bits of the device status word */
@@ -64,6 +65,27 @@ int mq_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, const
                    int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
                    float* logits_ws, size_t logits_ws_bytes, int64_t* ids64, int32_t* ids32,
                    float* weights, void* stream);
+
+/* Router for callers that cannot allocate.  No counterpart in the reference (its router lets
+ * torch allocate whatever it needs); same results as mq_router_topk, bit for bit.
+ *
+ * Meant for callers that cannot give this library a workspace: code that runs where the CUDA
+ * allocator must not be called, a foreign-language host (cgo, JNI, a plugin) that owns only its
+ * input and output buffers, a process whose pool already holds all device memory.  The logits
+ * scratch is an 8 MiB array built into the library image (each GPU that loads the library keeps it
+ * until the process exits); the call itself performs no cudaMalloc / cudaFree and calls no
+ * allocating routine.  The caller still passes inputs and outputs.
+ *   - Limit: mq_router_workspace_bytes(T, H, E) <= 8 MiB (with 128 experts: any batch up to
+ *     16384 tokens); larger requests return MQ_ERR_STATIC_SCRATCH_EXCEEDED, nothing launched.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the last call's contents.  Nothing in
+ *     it needs clearing (every element read is written first by the same call), but two calls
+ *     whose kernels overlap on the GPU (different streams, no ordering) race on it: order them.
+ */
+int mq_router_topk_static(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
+                          int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
+                          int64_t* ids64, int32_t* ids32, float* weights, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Permute plan.  Replaces the index work of moe_permute / moe_unpermute

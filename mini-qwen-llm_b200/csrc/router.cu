@@ -6,6 +6,8 @@
 // fp32, so the only rounding is the running sum) into a [T,E] fp32 workspace, then one warp per
 // token for softmax + selection.  Tensor cores are deliberately not used for the logits: expert
 // ids must equal those of an fp32 reference, and the adjacent-score gaps are a few fp32 ulp.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mq {
@@ -303,4 +305,65 @@ extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_d
   else if (E <= 512) launch_topk<16>(logits_ws, slices, bias, T, e, k, renormalize, ids64, ids32, weights, st);
   else launch_topk<32>(logits_ws, slices, bias, T, e, k, renormalize, ids64, ids32, weights, st);
   return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Router without a caller-provided workspace.
+//
+// Some callers cannot hand this library scratch memory because they cannot allocate at the moment
+// of the call: a serving loop that runs inside a region where the CUDA allocator must not be
+// touched, a host runtime (cgo, JNI, a plugin sandbox) that was given a fixed set of device buffers
+// for inputs and outputs and nothing else, or a process whose memory pool already owns the whole
+// device.  For them the logits scratch lives in the library image itself: a file-scope device
+// array that every GPU loading the library holds until the process exits.
+//
+// Host code must not pass the array's name to a kernel: on the host that name is only a stand-in
+// for the symbol, not a device address.  The address is looked up once per device with
+// cudaGetSymbolAddress while that device is current, and that pointer is what the kernels get.
+constexpr size_t R_STATIC_SCRATCH_BYTES = (size_t)8 << 20;   // 8 MiB: any batch up to 16384 tokens at 128 experts
+static __device__ __align__(256) float g_router_static_scratch[R_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+namespace mq {
+namespace {
+constexpr int kMaxDevices = 64;
+
+// Device address of the scratch array on the current device (set-up on the first call per device).
+float* static_scratch_for_current_device(int* status) {
+  static std::mutex mu;
+  static float* addr[kMaxDevices] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    if (e != cudaSuccess) set_last_cuda_error(e);
+    *status = MQ_ERR_LAUNCH_FAILED;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_router_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_last_cuda_error(e);
+      *status = MQ_ERR_LAUNCH_FAILED;
+      return nullptr;
+    }
+    addr[dev] = static_cast<float*>(p);
+  }
+  return addr[dev];
+}
+}  // namespace
+}  // namespace mq
+
+extern "C" int mq_router_topk_static(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
+                                     int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
+                                     int64_t* ids64, int32_t* ids32, float* weights, void* stream) {
+  if (T > 0 && H > 0 && E > 0 && mq_router_workspace_bytes(T, H, E) > R_STATIC_SCRATCH_BYTES)
+    return MQ_ERR_STATIC_SCRATCH_EXCEEDED;
+  int status = MQ_OK;
+  float* scratch = mq::static_scratch_for_current_device(&status);
+  if (scratch == nullptr) return status;
+  // The logits kernel writes every element of the slices it uses before the selection kernel reads
+  // them, so nothing in the array has to start at zero and the previous call's contents are harmless.
+  return mq_router_topk(x, x_dtype, w, w_dtype, bias, T, H, E, K, renormalize, scratch, R_STATIC_SCRATCH_BYTES,
+                        ids64, ids32, weights, stream);
 }

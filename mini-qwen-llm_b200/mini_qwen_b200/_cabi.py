@@ -25,6 +25,7 @@ PROTOTYPES = {
     "mq_last_cuda_error": (c_char_p, []),
     "mq_router_workspace_bytes": (c_size_t, [_L, _L, _L]),
     "mq_router_topk": (c_int, [_P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, c_size_t, _P, _P, _P, _P]),
+    "mq_router_topk_static": (c_int, [_P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _P, _P]),
     "mq_permute_workspace_bytes": (c_size_t, [_L, _L]),
     "mq_permute_plan": (c_int, [_P, _I, _L, _L, _L, _P, _P, _P, _P, _P, c_size_t, _P]),
     "mq_gather_rows": (c_int, [_P, _I, _P, _L, _L, _L, _P, _P]),
@@ -93,5 +94,5 @@ def check(status: int, what: str) -> None:
     msg = lib.mq_status_string(status).decode()
     if status == 4:
         msg += ": " + lib.mq_last_cuda_error().decode()
-    exc = ValueError if status in (1, 2, 3) else RuntimeError
+    exc = ValueError if status in (1, 2, 3, 6) else RuntimeError
     raise exc(f"{what}: {msg} (mq_status {status})")
