@@ -100,13 +100,16 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
-def build_dense_block(lay, device):
+def build_dense_block(lay, device, rank=0, world=1, group=None):
+    """The layer's experts [rank*E/world, (rank+1)*E/world) on `device` (all of them when world == 1)."""
     from mini_qwen_b200 import Qwen3MoEConfig
     from mini_qwen_b200.model.layers import Qwen3MoEBlock
 
     cfg = Qwen3MoEConfig(hidden_size=H, intermediate_size=I, num_experts=E, num_experts_per_tok=TOPK)
-    w13 = torch.cat([lay.gate, lay.up], dim=1).to(device)
-    blk = Qwen3MoEBlock.from_stacked(cfg, lay.router.to(device), w13, lay.down.to(device))
+    el = E // world
+    lo, hi = rank * el, (rank + 1) * el
+    w13 = torch.cat([lay.gate[lo:hi], lay.up[lo:hi]], dim=1).to(device)
+    blk = Qwen3MoEBlock.from_stacked(cfg, lay.router.to(device), w13, lay.down[lo:hi].to(device), ep_group=group)
     return blk
 
 
@@ -166,8 +169,10 @@ def run_ours(args):
     _cabi.load()
 
     lay = synthetic.dense_layer(1, T_PREFILL, H, E, TOPK, I, torch.bfloat16)
-    blk = build_dense_block(lay, dev)
+    blk = build_dense_block(lay, dev, rank, world, dist.group.WORLD if world > 1 else None)
     T = T_PREFILL
+    if rank > 0:   # every rank routes its own tokens (same distribution, different draw)
+        lay.x = torch.randn(T, H, generator=torch.Generator().manual_seed(1000 + rank)).to(torch.bfloat16)
     x_host = lay.x.pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
     x_dev = lay.x.to(dev)
@@ -254,7 +259,9 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"bf16 prefill MoE layer T={T} per GPU, H={H} E={E} top{TOPK} I={I} (seed 1)",
                    "l2": "per-step working set 1.2 GB of expert weights > 126 MB L2; no flush needed",
-                   "parallelism": "single GPU" if world == 1 else f"{world} replicas"},
+                   "parallelism": "single GPU" if world == 1 else
+                   f"expert parallel ep{world}: {E // world} experts per GPU, {T} tokens per GPU, "
+                   "NCCL all-to-all dispatch and combine"},
         "roofline": roofline, "cpu_baseline": cpu_base,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": e2e_ms / args.steps},

@@ -123,11 +123,15 @@ int mq_unpermute_combine(const void* rows, int dtype, const float* weights, cons
  * out[off[e]:off[e+1], :] = a[off[e]:off[e+1], :] . w[e]^T with fp32 accumulation.
  *   a [S,Kd], w [E,N,Kd], out [S,N], all of type `dtype`; offsets int32 [E+1].
  * Rows of `out` that belong to no expert are not written.
+ * weight_period: group e uses weight matrix e % weight_period (w then holds weight_period matrices).
+ * Plain use passes weight_period = E.  Expert parallelism passes the local expert count: the rows a
+ * rank receives are grouped by (source rank, local expert), i.e. G * E_local groups over E_local
+ * weight matrices.  The same argument has the same meaning in the calls below.
  * bf16 with Kd % 64 == 0 and N % 128 == 0 runs on the tcgen05/TMEM kernel, everything else on
  * a generic tiled kernel (Kd % 8 == 0 for 16-bit types, % 4 for fp32).
  */
 int mq_grouped_gemm(const void* a, const void* w, const int32_t* offsets,
-                    int64_t S, int64_t E, int64_t N, int64_t Kd, int dtype,
+                    int64_t S, int64_t E, int64_t weight_period, int64_t N, int64_t Kd, int dtype,
                     void* out, int32_t* d_status, void* stream);
 
 /* Fused gate/up projection with SwiGLU. Replaces _ExpertMLP's first half
@@ -137,7 +141,7 @@ int mq_grouped_gemm(const void* a, const void* w, const int32_t* offsets,
  *   a [S,H], w_gate_up [E, 2*I, H] (gate rows first, then up rows), h [S,I].
  */
 int mq_grouped_swiglu(const void* a, const void* w_gate_up, const int32_t* offsets,
-                      int64_t S, int64_t E, int64_t I, int64_t H, int dtype,
+                      int64_t S, int64_t E, int64_t weight_period, int64_t I, int64_t H, int dtype,
                       void* h, int32_t* d_status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
@@ -153,7 +157,7 @@ int mq_grouped_swiglu(const void* a, const void* w_gate_up, const int32_t* offse
  */
 int mq_w4a16_grouped_gemm(const void* x, const int32_t* qweight, const void* scales,
                           const int32_t* qzeros, const int32_t* offsets,
-                          int64_t S, int64_t E, int64_t N, int64_t Kd, int64_t group_size,
+                          int64_t S, int64_t E, int64_t weight_period, int64_t N, int64_t Kd, int64_t group_size,
                           void* out, void* stream);
 
 /* Fused W4A16 gate/up projection with SwiGLU (bf16 rounding after gate, silu, up and the
@@ -162,7 +166,7 @@ int mq_w4a16_grouped_swiglu(const void* x,
                             const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
                             const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
                             const int32_t* offsets,
-                            int64_t S, int64_t E, int64_t I, int64_t H, int64_t group_size,
+                            int64_t S, int64_t E, int64_t weight_period, int64_t I, int64_t H, int64_t group_size,
                             void* h, void* stream);
 
 #ifdef __cplusplus

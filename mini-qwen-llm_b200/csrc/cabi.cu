@@ -7,11 +7,12 @@ static thread_local cudaError_t g_last_error = cudaSuccess;
 void set_last_cuda_error(cudaError_t e) { g_last_error = e; }
 
 int grouped_gemm_generic_dispatch(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E,
-                                  int64_t N, int64_t Kd, int dtype, bool swiglu, void* out, cudaStream_t st);
+                                  int64_t period, int64_t N, int64_t Kd, int dtype, bool swiglu, void* out,
+                                  cudaStream_t st);
 
 // tcgen05 kernel (bf16). Returns MQ_ERR_UNSUPPORTED_SHAPE when the shape is outside its cover.
-int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t N,
-                     int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st);
+int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t period,
+                     int64_t N, int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st);
 bool tc5_covers(int64_t S, int64_t E, int64_t N, int64_t Kd, bool swiglu);
 
 }  // namespace mq
@@ -35,27 +36,29 @@ extern "C" const char* mq_status_string(int status) {
 
 extern "C" const char* mq_last_cuda_error(void) { return cudaGetErrorString(mq::g_last_error); }
 
-static int grouped_common(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t N,
-                          int64_t Kd, int dtype, bool swiglu, void* out, int32_t* d_status, void* stream) {
+static int grouped_common(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E,
+                          int64_t period, int64_t N, int64_t Kd, int dtype, bool swiglu, void* out,
+                          int32_t* d_status, void* stream) {
   using namespace mq;
   if (S < 0 || E <= 0 || N <= 0 || Kd <= 0 || !valid_dtype(dtype)) return MQ_ERR_INVALID_ARGUMENT;
+  if (period <= 0 || period > E) return MQ_ERR_INVALID_ARGUMENT;
   if (S >= (int64_t)1 << 31) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (S == 0) return MQ_OK;
   if (!a || !w || !offsets || !out) return MQ_ERR_INVALID_ARGUMENT;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == MQ_BF16 && tc5_covers(S, E, N, Kd, swiglu) && aligned16(a) && aligned16(w) && aligned16(out))
-    return grouped_gemm_tc5(a, w, offsets, S, E, N, Kd, swiglu, out, d_status, st);
-  return grouped_gemm_generic_dispatch(a, w, offsets, S, E, N, Kd, dtype, swiglu, out, st);
+  if (dtype == MQ_BF16 && tc5_covers(S, period, N, Kd, swiglu) && aligned16(a) && aligned16(w) && aligned16(out))
+    return grouped_gemm_tc5(a, w, offsets, S, E, period, N, Kd, swiglu, out, d_status, st);
+  return grouped_gemm_generic_dispatch(a, w, offsets, S, E, period, N, Kd, dtype, swiglu, out, st);
 }
 
 extern "C" int mq_grouped_gemm(const void* a, const void* w, const int32_t* offsets,
-                               int64_t S, int64_t E, int64_t N, int64_t Kd, int dtype,
+                               int64_t S, int64_t E, int64_t weight_period, int64_t N, int64_t Kd, int dtype,
                                void* out, int32_t* d_status, void* stream) {
-  return grouped_common(a, w, offsets, S, E, N, Kd, dtype, false, out, d_status, stream);
+  return grouped_common(a, w, offsets, S, E, weight_period, N, Kd, dtype, false, out, d_status, stream);
 }
 
 extern "C" int mq_grouped_swiglu(const void* a, const void* w_gate_up, const int32_t* offsets,
-                                 int64_t S, int64_t E, int64_t I, int64_t H, int dtype,
+                                 int64_t S, int64_t E, int64_t weight_period, int64_t I, int64_t H, int dtype,
                                  void* h, int32_t* d_status, void* stream) {
-  return grouped_common(a, w_gate_up, offsets, S, E, I, H, dtype, true, h, d_status, stream);
+  return grouped_common(a, w_gate_up, offsets, S, E, weight_period, I, H, dtype, true, h, d_status, stream);
 }

@@ -64,7 +64,7 @@ __device__ bool locate_tile(const int32_t* offsets, int E, int tile, int tm, int
 template <typename T, bool SWIGLU>
 __global__ void __launch_bounds__(G_THREADS)
 grouped_gemm_generic(const T* __restrict__ a, const T* __restrict__ w, const int32_t* __restrict__ offsets,
-                     int E, int64_t N, int64_t Kd, int vec_ok, T* __restrict__ out) {
+                     int E, int period, int64_t N, int64_t Kd, int vec_ok, T* __restrict__ out) {
   // w is [E, N, Kd]; with SWIGLU it is [E, 2N, Kd] (gate rows, then up rows) and out is [S, N].
   __shared__ __align__(16) float As[G_KC][G_PITCH];
   __shared__ __align__(16) float Bs[SWIGLU ? 2 : 1][G_KC][G_PITCH];
@@ -83,7 +83,7 @@ grouped_gemm_generic(const T* __restrict__ a, const T* __restrict__ w, const int
   const bool b_in = n0 + lr < N;
   const size_t a_base = (size_t)(row_lo + lr) * Kd;
   const int64_t w_rows = SWIGLU ? 2 * N : N;
-  const size_t b_base = ((size_t)e * w_rows + n0 + lr) * Kd;
+  const size_t b_base = ((size_t)(e % period) * w_rows + n0 + lr) * Kd;
   const size_t b2_base = b_base + (size_t)N * Kd;
 
   float acc[SWIGLU ? 2 : 1][4][4];
@@ -140,27 +140,28 @@ grouped_gemm_generic(const T* __restrict__ a, const T* __restrict__ w, const int
 }
 
 template <typename T>
-int launch_generic(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t N,
-                   int64_t Kd, bool swiglu, void* out, cudaStream_t st) {
+int launch_generic(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t period,
+                   int64_t N, int64_t Kd, bool swiglu, void* out, cudaStream_t st) {
   const int64_t tiles = (S + G_TM - 1) / G_TM + E;
   dim3 grid((unsigned)tiles, (unsigned)((N + G_TN - 1) / G_TN));
   const int vec_ok = (Kd % 4 == 0) && aligned16(a) && aligned16(w);
   if (swiglu)
     grouped_gemm_generic<T, true><<<grid, G_THREADS, 0, st>>>(reinterpret_cast<const T*>(a),
-        reinterpret_cast<const T*>(w), offsets, (int)E, N, Kd, vec_ok, reinterpret_cast<T*>(out));
+        reinterpret_cast<const T*>(w), offsets, (int)E, (int)period, N, Kd, vec_ok, reinterpret_cast<T*>(out));
   else
     grouped_gemm_generic<T, false><<<grid, G_THREADS, 0, st>>>(reinterpret_cast<const T*>(a),
-        reinterpret_cast<const T*>(w), offsets, (int)E, N, Kd, vec_ok, reinterpret_cast<T*>(out));
+        reinterpret_cast<const T*>(w), offsets, (int)E, (int)period, N, Kd, vec_ok, reinterpret_cast<T*>(out));
   return check_launch();
 }
 
 }  // namespace
 
 int grouped_gemm_generic_dispatch(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E,
-                                  int64_t N, int64_t Kd, int dtype, bool swiglu, void* out, cudaStream_t st) {
-  if (dtype == MQ_F32) return launch_generic<float>(a, w, offsets, S, E, N, Kd, swiglu, out, st);
-  if (dtype == MQ_BF16) return launch_generic<__nv_bfloat16>(a, w, offsets, S, E, N, Kd, swiglu, out, st);
-  return launch_generic<__half>(a, w, offsets, S, E, N, Kd, swiglu, out, st);
+                                  int64_t period, int64_t N, int64_t Kd, int dtype, bool swiglu, void* out,
+                                  cudaStream_t st) {
+  if (dtype == MQ_F32) return launch_generic<float>(a, w, offsets, S, E, period, N, Kd, swiglu, out, st);
+  if (dtype == MQ_BF16) return launch_generic<__nv_bfloat16>(a, w, offsets, S, E, period, N, Kd, swiglu, out, st);
+  return launch_generic<__half>(a, w, offsets, S, E, period, N, Kd, swiglu, out, st);
 }
 
 }  // namespace mq

@@ -149,7 +149,7 @@ struct TileCursor {
 template <bool SWIGLU>
 __global__ void __launch_bounds__(TC5_THREADS, 1)
 grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                        const int32_t* __restrict__ offsets, int E, int N, int Kd, int bn,
+                        const int32_t* __restrict__ offsets, int E, int period, int N, int Kd, int bn,
                         __nv_bfloat16* __restrict__ out, int32_t* d_status) {
   // N: output columns. SWIGLU: weights have 2N rows per expert, a tile = 128 gate + 128 up rows (bn = 256)
   // and produces 128 output columns.  Plain: a tile = bn (128 or 256) weight rows = bn output columns.
@@ -198,7 +198,7 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       for (int t = blockIdx.x; ok; t += gridDim.x) {
         int e, nt, row0, row_end;
         if (!cur.locate(t, e, nt, row0, row_end)) break;
-        const int wrow = e * w_rows_per_expert + nt * out_cols;
+        const int wrow = (e % period) * w_rows_per_expert + nt * out_cols;
         for (int kb = 0; kb < KB && ok; ++kb) {
           ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, d_status);
           if (!ok) break;
@@ -376,10 +376,10 @@ bool tc5_covers(int64_t S, int64_t E, int64_t N, int64_t Kd, bool swiglu) {
   return true;
 }
 
-int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t N,
-                     int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st) {
+int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t period,
+                     int64_t N, int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st) {
   CUtensorMap map_a, map_w;
-  const int64_t w_rows = E * (swiglu ? 2 * N : N);
+  const int64_t w_rows = period * (swiglu ? 2 * N : N);
   if (!make_map(&map_a, a, (uint64_t)S, (uint64_t)Kd) || !make_map(&map_w, w, (uint64_t)w_rows, (uint64_t)Kd))
     return MQ_ERR_DRIVER_ENTRY;
   const int bn = swiglu ? 256 : (N % 256 == 0 ? 256 : 128);
@@ -389,11 +389,11 @@ int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64
   // the attribute is per device; setting it is cheap, so it is set on every call
   if (swiglu) {
     cudaFuncSetAttribute(grouped_gemm_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    grouped_gemm_tc5_kernel<true><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_a, map_w, offsets, (int)E, (int)N,
+    grouped_gemm_tc5_kernel<true><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_a, map_w, offsets, (int)E, (int)period, (int)N,
         (int)Kd, bn, reinterpret_cast<__nv_bfloat16*>(out), d_status);
   } else {
     cudaFuncSetAttribute(grouped_gemm_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    grouped_gemm_tc5_kernel<false><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_a, map_w, offsets, (int)E, (int)N,
+    grouped_gemm_tc5_kernel<false><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_a, map_w, offsets, (int)E, (int)period, (int)N,
         (int)Kd, bn, reinterpret_cast<__nv_bfloat16*>(out), d_status);
   }
   return check_launch();

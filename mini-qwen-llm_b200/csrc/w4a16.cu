@@ -117,7 +117,7 @@ __device__ __forceinline__ void step_mma(W4Acc& a, const uint4& wv, const uint32
 template <bool SWIGLU>
 __global__ void __launch_bounds__(W4_WARPS * 32)
 w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
-                     const int32_t* __restrict__ offsets, int N, int Kd, int group,
+                     const int32_t* __restrict__ offsets, int period, int N, int Kd, int group,
                      __nv_bfloat16* __restrict__ out) {
   constexpr int NP = SWIGLU ? 2 : 1;
   __shared__ float red[W4_WARPS][NP][W4_NB * 8][32];
@@ -139,9 +139,10 @@ w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
   const int steps_per_group = group / 32;
   const int G = Kd / group;
 
-  const size_t qw_e = (size_t)e * (Kd / 8) * N;
-  const size_t sc_e = (size_t)e * G * N;
-  const size_t qz_e = (size_t)e * G * (N / 8);
+  const int we = e % period;            // weight set of this group
+  const size_t qw_e = (size_t)we * (Kd / 8) * N;
+  const size_t sc_e = (size_t)we * G * N;
+  const size_t qz_e = (size_t)we * G * (N / 8);
   const W4Proj proj[2] = {p0, p1};
 
   for (int r0 = 0; r0 < rows; r0 += 8 * W4_NB) {
@@ -249,8 +250,9 @@ w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
 }
 
 int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* offsets, int64_t S, int64_t E,
-              int64_t N, int64_t Kd, int64_t group, void* out, cudaStream_t st) {
+              int64_t period, int64_t N, int64_t Kd, int64_t group, void* out, cudaStream_t st) {
   if (S < 0 || E <= 0 || N <= 0 || Kd <= 0 || group <= 0) return MQ_ERR_INVALID_ARGUMENT;
+  if (period <= 0 || period > E) return MQ_ERR_INVALID_ARGUMENT;
   if (group % 32 != 0 || Kd % group != 0 || N % 8 != 0 || E > 65535) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (S == 0) return MQ_OK;
   if (!x || !p0.qw || !p0.sc || !p0.qz || !offsets || !out) return MQ_ERR_INVALID_ARGUMENT;
@@ -260,10 +262,10 @@ int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* o
   dim3 grid((unsigned)((N + 31) / 32), (unsigned)E);
   if (swiglu)
     w4a16_grouped_kernel<true><<<grid, W4_WARPS * 32, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), p0, p1,
-        offsets, (int)N, (int)Kd, (int)group, reinterpret_cast<__nv_bfloat16*>(out));
+        offsets, (int)period, (int)N, (int)Kd, (int)group, reinterpret_cast<__nv_bfloat16*>(out));
   else
     w4a16_grouped_kernel<false><<<grid, W4_WARPS * 32, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), p0, p0,
-        offsets, (int)N, (int)Kd, (int)group, reinterpret_cast<__nv_bfloat16*>(out));
+        offsets, (int)period, (int)N, (int)Kd, (int)group, reinterpret_cast<__nv_bfloat16*>(out));
   return check_launch();
 }
 
@@ -272,19 +274,21 @@ int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* o
 
 extern "C" int mq_w4a16_grouped_gemm(const void* x, const int32_t* qweight, const void* scales,
                                      const int32_t* qzeros, const int32_t* offsets,
-                                     int64_t S, int64_t E, int64_t N, int64_t Kd, int64_t group_size,
-                                     void* out, void* stream) {
+                                     int64_t S, int64_t E, int64_t weight_period, int64_t N, int64_t Kd,
+                                     int64_t group_size, void* out, void* stream) {
   mq::W4Proj p{qweight, reinterpret_cast<const __nv_bfloat16*>(scales), qzeros};
-  return mq::launch_w4(x, p, p, false, offsets, S, E, N, Kd, group_size, out, reinterpret_cast<cudaStream_t>(stream));
+  return mq::launch_w4(x, p, p, false, offsets, S, E, weight_period, N, Kd, group_size, out,
+                       reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int mq_w4a16_grouped_swiglu(const void* x,
                                        const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
                                        const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
                                        const int32_t* offsets,
-                                       int64_t S, int64_t E, int64_t I, int64_t H, int64_t group_size,
-                                       void* h, void* stream) {
+                                       int64_t S, int64_t E, int64_t weight_period, int64_t I, int64_t H,
+                                       int64_t group_size, void* h, void* stream) {
   mq::W4Proj pg{qweight_gate, reinterpret_cast<const __nv_bfloat16*>(scales_gate), qzeros_gate};
   mq::W4Proj pu{qweight_up, reinterpret_cast<const __nv_bfloat16*>(scales_up), qzeros_up};
-  return mq::launch_w4(x, pg, pu, true, offsets, S, E, I, H, group_size, h, reinterpret_cast<cudaStream_t>(stream));
+  return mq::launch_w4(x, pg, pu, true, offsets, S, E, weight_period, I, H, group_size, h,
+                       reinterpret_cast<cudaStream_t>(stream));
 }

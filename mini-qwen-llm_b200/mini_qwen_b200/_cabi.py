@@ -30,10 +30,10 @@ PROTOTYPES = {
     "mq_permute_plan": (c_int, [_P, _I, _L, _L, _L, _P, _P, _P, _P, _P, c_size_t, _P]),
     "mq_gather_rows": (c_int, [_P, _I, _P, _L, _L, _L, _P, _P]),
     "mq_unpermute_combine": (c_int, [_P, _I, _P, _P, _L, _L, _L, _P, _P]),
-    "mq_grouped_gemm": (c_int, [_P, _P, _P, _L, _L, _L, _L, _I, _P, _P, _P]),
-    "mq_grouped_swiglu": (c_int, [_P, _P, _P, _L, _L, _L, _L, _I, _P, _P, _P]),
-    "mq_w4a16_grouped_gemm": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P, _P]),
-    "mq_w4a16_grouped_swiglu": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P, _P]),
+    "mq_grouped_gemm": (c_int, [_P, _P, _P, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
+    "mq_grouped_swiglu": (c_int, [_P, _P, _P, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
+    "mq_w4a16_grouped_gemm": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P]),
+    "mq_w4a16_grouped_swiglu": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P]),
 }
 
 _lib = None

@@ -25,20 +25,23 @@ def moe_grouped_gemm(
 
     Unlike the reference there is no CPU branch (``moe_grouped_gemm.py:124-125``): CPU tensors
     are an error.  Rows covered by no expert are zero, as in the reference's oracle.
+    ``expert_offsets`` may hold a multiple G of E groups (+1): group g then uses ``expert_weights[g % E]``
+    (rows received under expert parallelism are grouped by source rank, then local expert).
     ``status`` (int32 [1], optional) receives device-side error bits (a bounded wait that ran out).
     ``zero_init=False`` skips the zero fill when the offsets are known to cover every row."""
     _cabi.require_cuda(permuted_hidden, expert_weights, expert_offsets)
     assert permuted_hidden.dim() == 2 and expert_weights.dim() == 3
     assert permuted_hidden.dtype == expert_weights.dtype, "activations and weights must share a dtype"
     E, D, H = expert_weights.shape
-    assert permuted_hidden.shape[1] == H and expert_offsets.numel() == E + 1
+    groups = expert_offsets.numel() - 1       # == E, or G * E under expert parallelism (group g -> weight g % E)
+    assert permuted_hidden.shape[1] == H and groups >= E and groups % E == 0
     a = permuted_hidden.contiguous()
     w = expert_weights.contiguous()
     S = a.shape[0]
     out = (torch.zeros if zero_init else torch.empty)(S, D, dtype=a.dtype, device=a.device)
     if status is None:
         status = _status_word(a.device)
-    rc = _cabi.load().mq_grouped_gemm(_cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(_offsets32(expert_offsets)), S, E, D, H,
+    rc = _cabi.load().mq_grouped_gemm(_cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(_offsets32(expert_offsets)), S, groups, E, D, H,
                                       _cabi.dtype_code(a), _cabi.ptr(out), _cabi.ptr(status),
                                       _cabi.stream_ptr(a.device))
     _cabi.check(rc, "mq_grouped_gemm")
@@ -54,14 +57,15 @@ def moe_grouped_swiglu(permuted_hidden: torch.Tensor, gate_up_weights: torch.Ten
     rows first, then up rows."""
     _cabi.require_cuda(permuted_hidden, gate_up_weights, expert_offsets)
     E, I2, H = gate_up_weights.shape
-    assert I2 % 2 == 0 and permuted_hidden.shape[1] == H
+    groups = expert_offsets.numel() - 1
+    assert I2 % 2 == 0 and permuted_hidden.shape[1] == H and groups >= E and groups % E == 0
     a = permuted_hidden.contiguous()
     S = a.shape[0]
     h = (torch.zeros if zero_init else torch.empty)(S, I2 // 2, dtype=a.dtype, device=a.device)
     if status is None:
         status = _status_word(a.device)
     rc = _cabi.load().mq_grouped_swiglu(_cabi.ptr(a), _cabi.ptr(gate_up_weights), _cabi.ptr(_offsets32(expert_offsets)),
-                                        S, E, I2 // 2, H, _cabi.dtype_code(a), _cabi.ptr(h), _cabi.ptr(status),
+                                        S, groups, E, I2 // 2, H, _cabi.dtype_code(a), _cabi.ptr(h), _cabi.ptr(status),
                                         _cabi.stream_ptr(a.device))
     _cabi.check(rc, "mq_grouped_swiglu")
     _cabi.count_launches(1 if S else 0)

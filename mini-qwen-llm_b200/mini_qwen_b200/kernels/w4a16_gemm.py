@@ -40,11 +40,13 @@ def w4a16_grouped_gemm(x, qweight, scales, qzeros, expert_offsets, group_size: i
     qweight [E, K/8, N], scales [E, K/g, N], qzeros [E, K/g, N/8], offsets int32 [E+1]."""
     E = qweight.shape[0]
     K, N = _check_w4(x, qweight, scales, qzeros, group_size, E)
+    groups = expert_offsets.numel() - 1       # E, or G * E (group g -> weight set g % E)
+    assert groups >= E and groups % E == 0
     x = x.contiguous()
     S = x.shape[0]
     out = (torch.zeros if zero_init else torch.empty)(S, N, dtype=torch.bfloat16, device=x.device)
     rc = _cabi.load().mq_w4a16_grouped_gemm(_cabi.ptr(x), _cabi.ptr(qweight), _cabi.ptr(scales), _cabi.ptr(qzeros),
-                                            _cabi.ptr(expert_offsets), S, E, N, K, group_size, _cabi.ptr(out),
+                                            _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size, _cabi.ptr(out),
                                             _cabi.stream_ptr(x.device))
     _cabi.check(rc, "mq_w4a16_grouped_gemm")
     _cabi.count_launches(1 if S else 0)
@@ -56,12 +58,14 @@ def w4a16_grouped_swiglu(x, gate, up, expert_offsets, group_size: int = 128, zer
     E = gate[0].shape[0]
     K, N = _check_w4(x, *gate, group_size, E)
     _check_w4(x, *up, group_size, E)
+    groups = expert_offsets.numel() - 1
+    assert groups >= E and groups % E == 0
     x = x.contiguous()
     S = x.shape[0]
     h = (torch.zeros if zero_init else torch.empty)(S, N, dtype=torch.bfloat16, device=x.device)
     rc = _cabi.load().mq_w4a16_grouped_swiglu(_cabi.ptr(x), _cabi.ptr(gate[0]), _cabi.ptr(gate[1]), _cabi.ptr(gate[2]),
                                               _cabi.ptr(up[0]), _cabi.ptr(up[1]), _cabi.ptr(up[2]),
-                                              _cabi.ptr(expert_offsets), S, E, N, K, group_size, _cabi.ptr(h),
+                                              _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size, _cabi.ptr(h),
                                               _cabi.stream_ptr(x.device))
     _cabi.check(rc, "mq_w4a16_grouped_swiglu")
     _cabi.count_launches(1 if S else 0)

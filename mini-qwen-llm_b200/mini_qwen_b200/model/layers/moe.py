@@ -20,6 +20,7 @@ from ...kernels.moe_permute import gather_rows, moe_permute_plan
 from ...kernels.moe_router import moe_router
 from ...kernels.moe_unpermute import unpermute_combine
 from ...kernels.w4a16_gemm import w4a16_grouped_gemm, w4a16_grouped_swiglu
+from ... import parallel
 from .linear_w4a16 import LinearW4A16
 
 _PROJ = ("gate_proj", "up_proj", "down_proj")
@@ -46,9 +47,15 @@ class _ExpertMLP(nn.Module):
 
 
 class Qwen3MoEBlock(nn.Module):
-    """router -> permute -> grouped gate/up + SwiGLU -> grouped down -> weighted combine."""
+    """router -> permute -> grouped gate/up + SwiGLU -> grouped down -> weighted combine.
 
-    def __init__(self, config):
+    With ``ep_group`` (a ``torch.distributed`` process group of G ranks) the block is expert
+    parallel: it holds only the ``num_experts / G`` experts of its rank (``experts[j]`` is global
+    expert ``expert_offset + j``), routes its own tokens over all experts, and exchanges rows with
+    the other ranks in one all-to-all each way (see ``mini_qwen_b200.parallel``).
+    """
+
+    def __init__(self, config, ep_group=None):
         super().__init__()
         self.num_experts = config.num_experts
         self.num_experts_per_tok = config.num_experts_per_tok
@@ -56,8 +63,15 @@ class Qwen3MoEBlock(nn.Module):
         self._epoch = [0]
         self._stacked_epoch = -1
         self._stacks = None
+        self.ep_group = ep_group
+        self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
+        self.ep_rank = 0 if ep_group is None else torch.distributed.get_rank(ep_group)
+        if self.num_experts % self.ep_size != 0:
+            raise ValueError(f"{self.num_experts} experts do not shard evenly over {self.ep_size} ranks")
+        self.num_local_experts = self.num_experts // self.ep_size
+        self.expert_offset = self.ep_rank * self.num_local_experts
         self.gate = nn.Linear(config.hidden_size, config.num_experts, bias=False)
-        self.experts = nn.ModuleList([_ExpertMLP(config, self._epoch) for _ in range(config.num_experts)])
+        self.experts = nn.ModuleList([_ExpertMLP(config, self._epoch) for _ in range(self.num_local_experts)])
         self.router_bias = None       # optional fp32 [E] logit bias (not in the reference)
         self.kernel_events = None     # set to a list to collect (stage, start, end) CUDA events per forward
 
@@ -113,16 +127,18 @@ class Qwen3MoEBlock(nn.Module):
 
     @classmethod
     def from_stacked(cls, config, router_weight: torch.Tensor, gate_up_proj: torch.Tensor,
-                     down_proj: torch.Tensor) -> "Qwen3MoEBlock":
+                     down_proj: torch.Tensor, ep_group=None) -> "Qwen3MoEBlock":
         """Builds a dense block from expert-major tensors without copying them:
         ``router_weight`` [E, H], ``gate_up_proj`` [E, 2I, H] (gate rows, then up rows: the fused
         layout of HF Qwen3-MoE checkpoints), ``down_proj`` [E, H, I].  The per-expert modules become
-        views of the given tensors."""
+        views of the given tensors.  With ``ep_group`` the expert tensors hold this rank's experts
+        only (``num_experts / G`` of them); the router weight always covers all experts."""
         E, I2, H = gate_up_proj.shape
-        assert E == config.num_experts and I2 == 2 * config.intermediate_size and H == config.hidden_size
-        assert tuple(down_proj.shape) == (E, H, I2 // 2) and tuple(router_weight.shape) == (E, H)
         with torch.device("meta"):
-            blk = cls(config)
+            blk = cls(config, ep_group=ep_group)
+        assert E == blk.num_local_experts and I2 == 2 * config.intermediate_size and H == config.hidden_size
+        assert tuple(down_proj.shape) == (E, H, I2 // 2)
+        assert tuple(router_weight.shape) == (config.num_experts, H)
         w13, w2 = gate_up_proj.contiguous(), down_proj.contiguous()
         blk.gate.weight = nn.Parameter(router_weight, requires_grad=False)
         inter = I2 // 2
@@ -155,7 +171,14 @@ class Qwen3MoEBlock(nn.Module):
         _, weights, ids32 = run("router", moe_router, x2d, self.gate.weight, K, bias=self.router_bias,
                                 renormalize=self.norm_topk_prob, return_int32_ids=True)
         perm, inv, off32, _ = run("permute_plan", moe_permute_plan, ids32, E, want_int64_offsets=False)
+        plan = None
+        if self.ep_size > 1:
+            all_counts = parallel.gather_counts(off32[1:] - off32[:-1], self.ep_group)
         permuted = run("gather_rows", gather_rows, x2d, perm, K)
+        if self.ep_size > 1:
+            plan = parallel.make_plan(all_counts, self.ep_rank)
+            permuted = run("dispatch", parallel.dispatch, permuted, plan, self.ep_group)
+            off32 = plan.seg_offsets
         if st["w4"]:
             # the offsets of a routing cover every slot, so no output needs a zero fill
             h = run("grouped_swiglu", w4a16_grouped_swiglu, permuted, st["gate_proj"], st["up_proj"], off32,
@@ -165,6 +188,8 @@ class Qwen3MoEBlock(nn.Module):
         else:
             h = run("grouped_swiglu", moe_grouped_swiglu, permuted, st["w13"], off32, zero_init=False)
             out_perm = run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False)
+        if plan is not None:
+            out_perm = run("combine", parallel.combine, out_perm, plan, self.ep_group)
         out = run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K)
         return out.reshape(shape)
 

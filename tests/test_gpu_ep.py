@@ -1,0 +1,85 @@
+"""Expert parallelism on 2+ GPUs: one process per GPU over NCCL; every rank's output must match the
+single-process CPU oracle on the concatenated batch, with routing bit-exact.  Skipped with one GPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, w4):
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for p in (root, os.path.join(root, "mini-qwen-llm_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    from mini_qwen_b200 import Qwen3MoEConfig, synthetic
+    from mini_qwen_b200.kernels import moe_router
+    from mini_qwen_b200.model.layers import LinearW4A16, Qwen3MoEBlock
+    from oracle import moe_oracle as O
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=dev)
+    try:
+        T_local, H, E, K, I = 300, 512, 16, 4, 256
+        el = E // world
+        lo, hi = rank * el, (rank + 1) * el
+        cfg = Qwen3MoEConfig(hidden_size=H, intermediate_size=I, num_experts=E, num_experts_per_tok=K)
+        bias = synthetic.zipf_router_bias(3, E, strength=2.0)
+        if not w4:
+            lay = synthetic.dense_layer(21, T_local * world, H, E, K, I, torch.bfloat16)
+            w13 = torch.cat([lay.gate[lo:hi], lay.up[lo:hi]], dim=1).to(dev)
+            blk = Qwen3MoEBlock.from_stacked(cfg, lay.router.to(dev), w13, lay.down[lo:hi].to(dev),
+                                             ep_group=dist.group.WORLD)
+            ref, ref_ids, _, _ = O.block_forward(lay.x, lay.router, lay.gate, lay.up, lay.down, K, True, bias)
+            router_w = lay.router
+        else:
+            lay = synthetic.w4a16_layer(22, T_local * world, H, E, K, I, group=128)
+            blk = Qwen3MoEBlock(cfg, ep_group=dist.group.WORLD)
+            for j, ex in enumerate(blk.experts):
+                e = lo + j
+                for name, p in (("gate_proj", lay.gate), ("up_proj", lay.up), ("down_proj", lay.down)):
+                    setattr(ex, name, LinearW4A16.from_gptq(p.qweight[e], p.qzeros[e], p.scales[e], 128, True))
+            router_w = lay.router.to(torch.bfloat16)
+            blk.gate.weight.data = router_w
+            blk = blk.to(dev)
+
+            def fn(e, x_e):
+                trios = [O.gptq_buffers(p.qweight[e], p.qzeros[e], p.scales[e]) for p in (lay.gate, lay.up, lay.down)]
+                return O.w4a16_expert(x_e, *trios, 128)
+            ref, ref_ids, _, _ = O.block_forward(lay.x, router_w, None, None, None, K, True, bias, expert_fn=fn)
+        blk.router_bias = bias.to(dev)
+        x = lay.x[rank * T_local:(rank + 1) * T_local].to(dev)
+        out = blk(x)
+        ids, _ = moe_router(x, router_w.to(dev), K, bias=bias.to(dev))
+        assert torch.equal(ids.cpu(), ref_ids[rank * T_local:(rank + 1) * T_local])
+        want = ref[rank * T_local:(rank + 1) * T_local].float()
+        got = out.cpu().float()
+        err = (got - want).abs()
+        ok = err <= 2e-3 * max(1.0, want.abs().max().item()) + 2e-2 * want.abs()
+        assert bool(ok.all()), f"rank {rank}: max err {err.max().item()}"
+        assert torch.equal(blk(x), out)                      # deterministic across calls
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("w4", [False, True])
+def test_expert_parallel_block_matches_oracle(w4):
+    world = torch.cuda.device_count()
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = 2 if world < 4 else 4
+    mp.spawn(_worker, args=(world, _free_port(), w4), nprocs=world, join=True)

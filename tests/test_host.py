@@ -150,7 +150,7 @@ def test_argument_checks_return_status_without_a_gpu():
     assert lib.mq_router_topk(None, 7, None, 0, None, 4, 32, 8, 2, 0, None, 0, None, None, None, None) == 1   # dtype
     assert lib.mq_permute_plan(None, 1, 4, 2, 128, None, None, None, None, None, 0, None) == 1             # no offsets
     assert lib.mq_permute_plan(None, 1, 4, 2, 2048, None, None, None, None, None, 0, None) == 2            # E > 1024
-    assert lib.mq_w4a16_grouped_gemm(None, None, None, None, None, 4, 1, 8, 128, 48, None, None) == 2      # group % 32
+    assert lib.mq_w4a16_grouped_gemm(None, None, None, None, None, 4, 1, 1, 8, 128, 48, None, None) == 2      # group % 32
     assert lib.mq_unpermute_combine(None, 1, None, None, 4, 33, 64, None, None) == 2                        # K > 32
     assert lib.mq_permute_workspace_bytes(131072, 128) >= 64 * 128 * 4
 
