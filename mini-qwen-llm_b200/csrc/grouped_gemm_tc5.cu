@@ -3,18 +3,27 @@
 // Arithmetic follows mini_qwen/kernels/moe_grouped_gemm.py:17-37 (fp32 accumulation, bf16 result)
 // and mini_qwen/model/layers/moe.py:24-25 (bf16 rounding after gate, silu, up, product).
 //
-// Persistent kernel, one CTA per SM, 6 warps:
-//   warp 0   TMA producer: A tile = 128 expert-sorted rows x 64 k, B tile = 256 weight rows x 64 k
-//            (for SwiGLU: 128 gate rows followed by 128 up rows), 128-byte swizzle, 4-stage ring;
-//   warp 1   MMA issuer: one thread issues tcgen05.mma 128x256x16 (cta_group::1, kind::f16) into one
-//            of two 256-column TMEM accumulators, tcgen05.commit releases the ring slot / publishes
-//            the accumulator;
-//   warps 2-5 epilogue: tcgen05.ld (thread = row), SwiGLU or plain rounding, row-predicated
-//            16-byte stores; overlaps the next tile's main loop through the second accumulator.
-// Tiles are walked in (expert, n-tile, m-tile) order so that the CTAs working at the same time
-// share a weight tile (read once from HBM, then from L2).  The tile list is derived on the device
-// from the offsets; no host synchronisation.  A row tile that straddles the end of its expert
-// computes the extra rows and masks their stores; rows past the end of the matrix are TMA zero fill.
+// Orientation: the WEIGHT rows are the 128-lane M dimension of the MMA and the TOKENS are its N
+// dimension (16..256 in steps of 16).  An expert's row count is ragged; making it the N dimension
+// means a tile is exactly as wide as the expert needs (no 128-row padding), and a decode batch with
+// a handful of rows per expert still streams every weight byte exactly once.
+//
+// A tile = two weight sub-tiles of 128 rows that share one token tile:
+//   SwiGLU: 128 gate rows + the matching 128 up rows  -> 128 output columns of h
+//   plain : rows [f0, f0+128) and [f0+128, f0+256)    -> 256 output columns
+// so each token tile fetched through L2 feeds two MMAs (64 KB of operands per 1024 MMA cycles at
+// 256 tokens, against 48 KB per 512 cycles for a single 128x256 tile: the kernel is bound by the
+// per-SM L2 bandwidth, not by the tensor pipe).  The two fp32 accumulators take all 512 TMEM
+// columns, so a tile's epilogue does not overlap the next tile's MMAs; the TMA ring keeps loading
+// meanwhile and eight epilogue warps keep the drain short.
+//
+// Persistent kernel, one CTA per SM, 10 warps:
+//   warp 0     TMA producer (3-stage ring, 128-byte swizzle, K-major operands);
+//   warp 1     MMA issuer: one thread, tcgen05.mma.cta_group::1.kind::f16, M=128, N=tokens, K=16;
+//   warps 2-9  epilogue: tcgen05.ld (lane = output column, TMEM column = token), SwiGLU / rounding,
+//              stores of 32 adjacent columns per warp and token.
+// Tiles are walked in (expert, token tile, weight tile) order: CTAs running at the same time share
+// the token rows of an expert through L2 and every weight tile is read from HBM once.
 //
 // Every mbarrier wait is bounded: when it runs out the kernel sets MQ_DEV_WAIT_EXPIRED in the status
 // word, all roles leave their loops, and TMEM is freed before the CTA exits.
@@ -27,15 +36,20 @@
 namespace mq {
 namespace {
 
-constexpr int BM = 128;                 // rows (slots) per tile = TMEM lanes
+constexpr int TM = 128;                 // weight rows per sub-tile = TMEM lanes
 constexpr int BK = 64;                  // k per stage = one 128-byte swizzle span of bf16
-constexpr int BN_MAX = 256;             // accumulator columns per tile
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2;        // 16 KB
-constexpr int B_BYTES = BN_MAX * BK * 2;    // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
-constexpr int TC5_THREADS = 192;
+constexpr int TN_MAX = 256;             // tokens per tile (MMA N)
+constexpr int STAGES = 3;
+constexpr int A_BYTES = TM * BK * 2;            // 16 KB per weight sub-tile
+constexpr int B_BYTES = TN_MAX * BK * 2;        // 32 KB token tile
+constexpr int BOX_TOK = 64;                     // token rows per TMA box
+constexpr int BOX_TOK_BYTES = BOX_TOK * BK * 2; // 8 KB
+constexpr int STAGE_BYTES = 2 * A_BYTES + B_BYTES;
+constexpr int EPI_WARPS = 8;
+constexpr int TR_PITCH = 64;                    // bytes per token row of a warp's 32x32 bf16 transpose block
+constexpr int TR_BYTES = 32 * TR_PITCH;         // per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + EPI_WARPS * TR_BYTES;
+constexpr int TC5_THREADS = (2 + EPI_WARPS) * 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -93,7 +107,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
 
 // Instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t umma_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
 }
 
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
@@ -119,24 +133,77 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Walks the tile list in (expert, n-tile, m-tile) order. Every role keeps its own cursor.
+// SwiGLU of two accumulator pairs with the rounding points of the op-by-op bf16 path (g, silu(g), u
+// and the product are each rounded to bf16); exp and the reciprocal use the SFU approximations,
+// whose error (2^-21) is far below the bf16 rounding that follows.  Returns the packed bf16 pair.
+__device__ __forceinline__ uint32_t swiglu_pair(float g0, float g1, float u0, float u1) {
+  const __nv_bfloat162 gb = __floats2bfloat162_rn(g0, g1);
+  const __nv_bfloat162 ub = __floats2bfloat162_rn(u0, u1);
+  const float2 gf = __bfloat1622float2(gb);
+  const float2 uf = __bfloat1622float2(ub);
+  const float s0 = __fdividef(gf.x, 1.0f + __expf(-gf.x));
+  const float s1 = __fdividef(gf.y, 1.0f + __expf(-gf.y));
+  const float2 sf = __bfloat1622float2(__floats2bfloat162_rn(s0, s1));
+  const __nv_bfloat162 o = __floats2bfloat162_rn(sf.x * uf.x, sf.y * uf.y);
+  return *reinterpret_cast<const uint32_t*>(&o);
+}
+
+// Writes a warp's 32 (tokens) x 32 (output columns) block of bf16 values, held as one column per lane
+// (vals[j] = packed tokens 2j, 2j+1), to global memory as 64-byte row segments.  The block is transposed
+// through shared memory; on the way out 4 lanes share a token row (16 bytes each), so one store
+// instruction covers 8 full 64-byte segments.  dst points at column 0 of the block in token row 0;
+// rows >= valid_rows are not written.
+__device__ __forceinline__ void store_block_transposed(const uint32_t (&vals)[16], uint8_t* tbuf, int lane,
+                                                       __nv_bfloat16* dst, size_t row_stride, int valid_rows) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    *reinterpret_cast<uint16_t*>(tbuf + (2 * j) * TR_PITCH + 2 * lane) = (uint16_t)(vals[j] & 0xffffu);
+    *reinterpret_cast<uint16_t*>(tbuf + (2 * j + 1) * TR_PITCH + 2 * lane) = (uint16_t)(vals[j] >> 16);
+  }
+  __syncwarp();
+  const int piece = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = 8 * i + (lane >> 2);
+    if (row < valid_rows) {
+      const uint4 v = *reinterpret_cast<const uint4*>(tbuf + row * TR_PITCH + piece * 16);
+      *reinterpret_cast<uint4*>(dst + (size_t)row * row_stride + piece * 8) = v;
+    }
+  }
+  __syncwarp();
+}
+
+// One tile of work.
+struct Tile {
+  int expert;     // group index (weights: expert % period)
+  int wt;         // weight tile index
+  int tok0;       // first row of the token tile
+  int tok_end;    // one past the last valid row (end of the tile or of the expert)
+  int n_mma;      // MMA N: rows of the token tile rounded up to 16
+};
+
+// Walks the tile list in (expert, token tile, weight tile) order. Every role keeps its own cursor.
 struct TileCursor {
   const int32_t* off;
-  int E, NT;
+  int E, NWT;
   int e, base;      // first tile index of expert e
-  __device__ TileCursor(const int32_t* o, int E_, int NT_) : off(o), E(E_), NT(NT_), e(0), base(0) {}
+  __device__ TileCursor(const int32_t* o, int E_, int NWT_) : off(o), E(E_), NWT(NWT_), e(0), base(0) {}
   // Locates tile t (t must not decrease between calls). Returns false past the last tile.
-  __device__ bool locate(int t, int& expert, int& nt, int& row0, int& row_end) {
+  __device__ bool locate(int t, Tile& tile) {
     while (e < E) {
       const int lo = off[e], hi = off[e + 1];
-      const int mt = (hi - lo + BM - 1) / BM;
-      const int span = mt * NT;
+      const int n = hi - lo;
+      const int ntt = (n + TN_MAX - 1) / TN_MAX;
+      const int span = ntt * NWT;
       if (t < base + span) {
         const int local = t - base;
-        expert = e;
-        nt = local / mt;
-        row0 = lo + (local - nt * mt) * BM;
-        row_end = hi;
+        const int tt = local / NWT;
+        const int width = (((n + ntt - 1) / ntt) + 15) & ~15;     // balanced token tiles, multiple of 16
+        tile.expert = e;
+        tile.wt = local - tt * NWT;
+        tile.tok0 = lo + tt * width;
+        tile.tok_end = min(tile.tok0 + width, hi);
+        tile.n_mma = (tile.tok_end - tile.tok0 + 15) & ~15;
         return true;
       }
       base += span;
@@ -148,33 +215,33 @@ struct TileCursor {
 
 template <bool SWIGLU>
 __global__ void __launch_bounds__(TC5_THREADS, 1)
-grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                        const int32_t* __restrict__ offsets, int E, int period, int N, int Kd, int bn,
+grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                        const int32_t* __restrict__ offsets, int E, int period, int N, int Kd,
                         __nv_bfloat16* __restrict__ out, int32_t* d_status) {
-  // N: output columns. SWIGLU: weights have 2N rows per expert, a tile = 128 gate + 128 up rows (bn = 256)
-  // and produces 128 output columns.  Plain: a tile = bn (128 or 256) weight rows = bn output columns.
+  // N: output columns.  SWIGLU: the weights hold 2N rows per expert (gate rows, then up rows).
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;                 // 1024-byte aligned for the swizzle
   uint8_t* bar_mem = smem_raw + (tiles_base - raw) + STAGES * STAGE_BYTES;
   const uint32_t bars = tiles_base + STAGES * STAGE_BYTES;
-  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem ptr, abort
+  // barriers (8 bytes each): full[STAGES], empty[STAGES], tmem_full, tmem_empty; then tmem pointer, abort flag
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
-  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
-  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * (2 * STAGES + 4));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (2 * STAGES + 4) + 8);
+  const uint32_t tfull_bar = bars + 8u * (2 * STAGES);
+  const uint32_t tempty_bar = bars + 8u * (2 * STAGES + 1);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * (2 * STAGES + 2));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * (2 * STAGES + 2) + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int out_cols = SWIGLU ? 128 : bn;          // output columns per tile
-  const int NT = N / out_cols;
+  const int cols_per_tile = SWIGLU ? TM : 2 * TM;      // output columns per tile
+  const int NWT = (N + cols_per_tile - 1) / cols_per_tile;
   const int KB = Kd / BK;
   const int w_rows_per_expert = SWIGLU ? 2 * N : N;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 128); }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, EPI_WARPS * 32);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -191,28 +258,31 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      TileCursor cur(offsets, E, NT);
+      TileCursor cur(offsets, E, NWT);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      Tile tl;
       for (int t = blockIdx.x; ok; t += gridDim.x) {
-        int e, nt, row0, row_end;
-        if (!cur.locate(t, e, nt, row0, row_end)) break;
-        const int wrow = (e % period) * w_rows_per_expert + nt * out_cols;
+        if (!cur.locate(t, tl)) break;
+        const int f0 = tl.wt * cols_per_tile;
+        const int wbase = (tl.expert % period) * w_rows_per_expert;
+        const int wrow0 = wbase + f0;
+        const int wrow1 = SWIGLU ? wbase + N + f0 : wbase + f0 + TM;
+        const bool two = SWIGLU || (f0 + TM < N);
+        const int nbox = (tl.n_mma + BOX_TOK - 1) / BOX_TOK;
+        const uint32_t tx = (uint32_t)((two ? 2 : 1) * A_BYTES + nbox * BOX_TOK_BYTES);
         for (int kb = 0; kb < KB && ok; ++kb) {
           ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, d_status);
           if (!ok) break;
-          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
-          const uint32_t sb = sa + A_BYTES;
-          mbar_expect_tx(full_bar(stage), (uint32_t)(A_BYTES + bn * BK * 2));
-          tma_load_2d(sa, &map_a, full_bar(stage), kb * BK, row0);
-          if (SWIGLU) {
-            tma_load_2d(sb, &map_w, full_bar(stage), kb * BK, wrow);                     // 128 gate rows
-            tma_load_2d(sb + 128 * BK * 2, &map_w, full_bar(stage), kb * BK, wrow + N);  // 128 up rows
-          } else {
-            tma_load_2d(sb, &map_w, full_bar(stage), kb * BK, wrow);
-            if (bn == 256) tma_load_2d(sb + 128 * BK * 2, &map_w, full_bar(stage), kb * BK, wrow + 128);
-          }
+          const uint32_t sa0 = tiles_base + stage * STAGE_BYTES;
+          const uint32_t sa1 = sa0 + A_BYTES;
+          const uint32_t sb = sa0 + 2 * A_BYTES;
+          mbar_expect_tx(full_bar(stage), tx);
+          tma_load_2d(sa0, &map_w, full_bar(stage), kb * BK, wrow0);
+          if (two) tma_load_2d(sa1, &map_w, full_bar(stage), kb * BK, wrow1);
+          for (int b = 0; b < nbox; ++b)
+            tma_load_2d(sb + b * BOX_TOK_BYTES, &map_x, full_bar(stage), kb * BK, tl.tok0 + b * BOX_TOK);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -226,91 +296,93 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      TileCursor cur(offsets, E, NT);
-      const uint32_t idesc = umma_idesc(bn);
-      int stage = 0, acc = 0;
+      TileCursor cur(offsets, E, NWT);
+      int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      Tile tl;
       for (int t = blockIdx.x; ok; t += gridDim.x) {
-        int e, nt, row0, row_end;
-        if (!cur.locate(t, e, nt, row0, row_end)) break;
-        ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, d_status);
+        if (!cur.locate(t, tl)) break;
+        const bool two = SWIGLU || (tl.wt * cols_per_tile + TM < N);
+        const uint32_t idesc = umma_idesc(tl.n_mma);
+        ok = mbar_wait(tempty_bar, acc_phase ^ 1u, abort_flag, d_status);   // epilogue has drained TMEM
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_MAX);
         for (int kb = 0; kb < KB; ++kb) {
           ok = mbar_wait(full_bar(stage), phase, abort_flag, d_status);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
-          const uint64_t adesc = umma_desc(sa);
-          const uint64_t bdesc = umma_desc(sa + A_BYTES);
+          const uint32_t sa0 = tiles_base + stage * STAGE_BYTES;
+          const uint64_t a0 = umma_desc(sa0);
+          const uint64_t a1 = umma_desc(sa0 + A_BYTES);
+          const uint64_t bd = umma_desc(sa0 + 2 * A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // 16 k = 32 bytes along the swizzled row: +2 in the (address >> 4) field
-            umma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            umma_f16(tmem_base, a0 + 2u * k, bd + 2u * k, idesc, accum);
+            if (two) umma_f16(tmem_base + TN_MAX, a1 + 2u * k, bd + 2u * k, idesc, accum);
           }
           umma_commit(empty_bar(stage));          // frees the ring slot once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(tfull_bar(acc));              // accumulator complete
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
+        umma_commit(tfull_bar);                   // accumulators complete
+        acc_phase ^= 1u;
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    TileCursor cur(offsets, E, NT);
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    TileCursor cur(offsets, E, NWT);
     const int quad = warp & 3;                     // TMEM lane quadrant this warp may read
-    const int row_in_tile = quad * 32 + lane;
-    int acc = 0;
+    const int half = (warp - 2) >> 2;              // which 32-token chunks (even / odd) this warp drains
+    uint8_t* tbuf = bar_mem + 256 + (warp - 2) * TR_BYTES;
     uint32_t acc_phase = 0;
     bool ok = true;
+    Tile tl;
     for (int t = blockIdx.x; ok; t += gridDim.x) {
-      int e, nt, row0, row_end;
-      if (!cur.locate(t, e, nt, row0, row_end)) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(acc), acc_phase, abort_flag, d_status));
+      if (!cur.locate(t, tl)) break;
+      ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar, acc_phase, abort_flag, d_status));
       if (!ok) break;
       tc_fence_after();
-      const int row = row0 + row_in_tile;
-      const bool row_ok = row < row_end;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN_MAX);
-      __nv_bfloat16* orow = out + (size_t)row * N + (size_t)nt * out_cols;
-      for (int c = 0; c < out_cols; c += 32) {
-        uint32_t g[32];
-        uint32_t packed[16];
-        tmem_ld32(taddr + c, g);
+      const int f0 = tl.wt * cols_per_tile;
+      const bool two = SWIGLU || (f0 + TM < N);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      const int ntok = tl.tok_end - tl.tok0;
+      for (int c = half * 32; c < tl.n_mma; c += 64) {
+        // lane = output column quad*32+lane of the sub-tile; registers = 32 consecutive tokens
+        uint32_t r0[32], r1[32], packed[16];
+        tmem_ld32(taddr + c, r0);
+        if (two) tmem_ld32(taddr + TN_MAX + c, r1);
+        tmem_ld_wait();
+        const int valid = ntok - c;                    // token rows of this chunk that exist
+        __nv_bfloat16* oblk = out + (size_t)(tl.tok0 + c) * N + f0 + quad * 32;
         if (SWIGLU) {
-          uint32_t u[32];
-          tmem_ld32(taddr + 128 + c, u);
-          tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float o0 = swiglu_rounded<__nv_bfloat16>(__uint_as_float(g[2 * j]), __uint_as_float(u[2 * j]));
-            float o1 = swiglu_rounded<__nv_bfloat16>(__uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1]));
-            __nv_bfloat162 p = __floats2bfloat162_rn(o0, o1);
-            packed[j] = *reinterpret_cast<uint32_t*>(&p);
-          }
+          for (int j = 0; j < 16; ++j)
+            packed[j] = swiglu_pair(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]),
+                                    __uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+          store_block_transposed(packed, tbuf, lane, oblk, (size_t)N, valid);
         } else {
-          tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(g[2 * j]), __uint_as_float(g[2 * j + 1]));
-            packed[j] = *reinterpret_cast<uint32_t*>(&p);
+            const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+            packed[j] = *reinterpret_cast<const uint32_t*>(&p);
           }
-        }
-        if (row_ok) {
-          uint4* dst = reinterpret_cast<uint4*>(orow + c);
+          store_block_transposed(packed, tbuf, lane, oblk, (size_t)N, valid);
+          if (two) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v)
-            dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            for (int j = 0; j < 16; ++j) {
+              const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+              packed[j] = *reinterpret_cast<const uint32_t*>(&p);
+            }
+            store_block_transposed(packed, tbuf, lane, oblk + TM, (size_t)N, valid);
+          }
         }
       }
       tc_fence_before();
-      mbar_arrive(tempty_bar(acc));
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      mbar_arrive(tempty_bar);
+      acc_phase ^= 1u;
     }
   }
 
@@ -340,13 +412,13 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D bf16 row-major [rows, cols] tensor, box = 64 columns x 128 rows, 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
+// 2-D bf16 row-major [rows, cols] tensor, box = 64 columns x box_rows rows, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, 128u};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -378,23 +450,24 @@ bool tc5_covers(int64_t S, int64_t E, int64_t N, int64_t Kd, bool swiglu) {
 
 int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t period,
                      int64_t N, int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st) {
-  CUtensorMap map_a, map_w;
+  CUtensorMap map_x, map_w;
   const int64_t w_rows = period * (swiglu ? 2 * N : N);
-  if (!make_map(&map_a, a, (uint64_t)S, (uint64_t)Kd) || !make_map(&map_w, w, (uint64_t)w_rows, (uint64_t)Kd))
+  if (!make_map(&map_x, a, (uint64_t)S, (uint64_t)Kd, BOX_TOK) ||
+      !make_map(&map_w, w, (uint64_t)w_rows, (uint64_t)Kd, TM))
     return MQ_ERR_DRIVER_ENTRY;
-  const int bn = swiglu ? 256 : (N % 256 == 0 ? 256 : 128);
-  const int out_cols = swiglu ? 128 : bn;
-  const int64_t tiles_max = ((S + BM - 1) / BM + E) * (N / out_cols);
+  const int64_t cols_per_tile = swiglu ? TM : 2 * TM;
+  const int64_t nwt = (N + cols_per_tile - 1) / cols_per_tile;
+  const int64_t tiles_max = ((S + TN_MAX - 1) / TN_MAX + E) * nwt;
   const int grid = (int)(tiles_max < sm_count() ? tiles_max : sm_count());
   // the attribute is per device; setting it is cheap, so it is set on every call
   if (swiglu) {
     cudaFuncSetAttribute(grouped_gemm_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    grouped_gemm_tc5_kernel<true><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_a, map_w, offsets, (int)E, (int)period, (int)N,
-        (int)Kd, bn, reinterpret_cast<__nv_bfloat16*>(out), d_status);
+    grouped_gemm_tc5_kernel<true><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_x, map_w, offsets, (int)E, (int)period,
+        (int)N, (int)Kd, reinterpret_cast<__nv_bfloat16*>(out), d_status);
   } else {
     cudaFuncSetAttribute(grouped_gemm_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    grouped_gemm_tc5_kernel<false><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_a, map_w, offsets, (int)E, (int)period, (int)N,
-        (int)Kd, bn, reinterpret_cast<__nv_bfloat16*>(out), d_status);
+    grouped_gemm_tc5_kernel<false><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_x, map_w, offsets, (int)E, (int)period,
+        (int)N, (int)Kd, reinterpret_cast<__nv_bfloat16*>(out), d_status);
   }
   return check_launch();
 }
