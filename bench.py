@@ -113,6 +113,80 @@ def build_dense_block(lay, device, rank=0, world=1, group=None):
     return blk
 
 
+def w4a16_decode_numbers(dev, peaks, iters=200, copies=8, batches=(1, 8, 16, 64)):
+    """W4A16 decode of the same layer shape: per batch size, the time of one block call under
+    CUDA-graph replay, rotating over `copies` independently drawn layers so that no weight byte is
+    served from L2 (a layer's active experts are 20-310 MB; 8 layers exceed the 126 MB L2 several
+    times over).  Algorithmic bytes = packed weights, scales and zero points of the experts hit
+    (2 451 456 B each) + router weight + activations in and out."""
+    from mini_qwen_b200 import Qwen3MoEConfig
+    from mini_qwen_b200.model.layers import LinearW4A16, Qwen3MoEBlock
+
+    cfg = Qwen3MoEConfig(hidden_size=H, intermediate_size=I, num_experts=E, num_experts_per_tok=TOPK)
+    gen = torch.Generator(device=dev).manual_seed(2)
+
+    def stack(kd, n):
+        qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (E, kd // 8, n), generator=gen, device=dev, dtype=torch.int32)
+        sc = (torch.rand(E, kd // 128, n, generator=gen, device=dev) * 0.015 + 0.005).to(torch.bfloat16)
+        qz = torch.randint(-2 ** 31, 2 ** 31 - 1, (E, kd // 128, n // 8), generator=gen, device=dev, dtype=torch.int32)
+        return qw, sc, qz
+
+    blocks = []
+    for _ in range(copies):
+        with torch.device("meta"):
+            blk = Qwen3MoEBlock(cfg)
+        blk.gate.weight = torch.nn.Parameter(
+            (torch.randn(E, H, generator=gen, device=dev) * 0.02).to(torch.bfloat16), requires_grad=False)
+        blk._stacks = {"w4": True, "group_size": 128, "gate_proj": stack(H, I), "up_proj": stack(H, I),
+                       "down_proj": stack(I, H)}
+        blk._ready = lambda st=blk._stacks: st          # stacks are installed directly (random packed words)
+        blocks.append(blk)
+
+    expert_bytes = 3 * (H * I // 2) + 2 * (H // 128) * I * 2 + (I // 128) * H * 2 \
+        + 2 * (H // 128) * (I // 8) * 4 + (I // 128) * (H // 8) * 4
+    out = []
+    for T in batches:
+        xs = [torch.randn(T, H, generator=gen, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        active = []
+        graphs = []
+        with torch.no_grad():
+            for blk, x in zip(blocks, xs):
+                blk(x)                                                   # warm-up, also sets kernel attributes
+                from mini_qwen_b200.kernels import moe_router
+                ids, _ = moe_router(x, blk.gate.weight, TOPK)
+                active.append(int(torch.unique(ids).numel()))
+            torch.cuda.synchronize()
+            for blk, x in zip(blocks, xs):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    blk(x)
+                graphs.append(g)
+            for g in graphs:
+                g.replay()
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for i in range(iters):
+                graphs[i % copies].replay()
+            e.record()
+            torch.cuda.synchronize()
+            us_graph = s.elapsed_time(e) * 1e3 / iters
+            s.record()
+            for i in range(iters):
+                blocks[i % copies](xs[i % copies])
+            e.record()
+            torch.cuda.synchronize()
+            us_eager = s.elapsed_time(e) * 1e3 / iters
+        a = sum(active) / len(active)
+        nbytes = a * expert_bytes + E * H * 2 + 2 * T * H * 2
+        gbs = nbytes / (us_graph * 1e-6) / 1e9
+        out.append({"T": T, "active_experts": a, "us_per_step_graph": us_graph, "us_per_step_eager": us_eager,
+                    "tokens_per_s": T / (us_graph * 1e-6), "algorithmic_mb": nbytes / 1e6, "hbm_gbs": gbs,
+                    "hbm_frac": gbs / peaks["hbm_gbs"]})
+        del graphs
+    return out
+
+
 def cpu_reference_tokens_per_s(lay, steps, warmup, sample_t):
     """The reference's per-expert-loop path (CPU restatement) on `sample_t`-token slices of the batch."""
     from oracle import moe_oracle as O
@@ -268,6 +342,10 @@ def run_ours(args):
         "gpu_launches": launches, "clocks": clocks.summary(),
         "kernels_ms": kern_ms,
     }
+    if world == 1 and not args.no_decode:
+        del blk
+        torch.cuda.empty_cache()
+        line["w4a16_decode"] = w4a16_decode_numbers(dev, peaks)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -280,6 +358,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the W4A16 decode numbers")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

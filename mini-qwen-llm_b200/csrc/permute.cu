@@ -12,7 +12,8 @@ namespace {
 
 constexpr int P_THREADS = 256;            // 8 warps
 constexpr int P_CHUNK = P_THREADS;        // slots ranked per step
-constexpr int P_SEG = 8 * P_CHUNK;        // slots per CTA
+constexpr int P_SEG = 2 * P_CHUNK;        // slots per CTA in the multi-CTA plan
+constexpr int P_SMALL = 8 * P_CHUNK;      // up to this many slots the whole plan runs in one CTA
 constexpr int P_MAX_E = 1024;
 
 template <bool IDS64>
@@ -265,7 +266,7 @@ extern "C" int mq_permute_plan(const void* ids, int ids_are_64, int64_t T, int64
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (S > 0 && (!ids || !perm || !inv)) return MQ_ERR_INVALID_ARGUMENT;
 
-  if (S <= P_SEG) {
+  if (S <= P_SMALL) {
     // also covers S == 0: the kernel then only writes zero offsets
     if (ids_are_64) permute_plan_small<true><<<1, P_THREADS, 0, st>>>(ids, S, (int)E, perm, inv, offsets64, offsets32);
     else permute_plan_small<false><<<1, P_THREADS, 0, st>>>(ids, S, (int)E, perm, inv, offsets64, offsets32);

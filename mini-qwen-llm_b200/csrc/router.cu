@@ -133,6 +133,99 @@ router_logits_tiled(const void* __restrict__ x, int xdt, const void* __restrict_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Tensor-core logits for 16-bit inputs of one type (bf16 x bf16 or fp16 x fp16), T > 64.
+// CTA = 32 tokens x 128 experts x one K slice; 8 warps, each 16 tokens x 32 experts of
+// mma.sync.m16n8k16 with fp32 accumulators.  Products of 16-bit inputs are exact in the tensor core;
+// to keep the accumulation as accurate as an fp32 FMA chain, a tensor-core accumulator only ever
+// sums 128 k (8 MMAs) and is then added to a master accumulator with an ordinary fp32 add.
+// Fragments are fetched with 16-byte loads: the order of k inside a 32-wide block is free as long
+// as both operands use the same one, so lane (g, kq) takes k = 8*kq .. 8*kq+7 of its row and feeds
+// {0,1 | 2,3} to the first MMA and {4,5 | 6,7} to the second.
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1, bool bf16) {
+  if (bf16)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int RM_TM = 32, RM_TE = 128, RM_THREADS = 256;
+
+__global__ void __launch_bounds__(RM_THREADS)
+router_logits_mma(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, int is_bf16,
+                  int64_t T, int64_t H, int64_t E, int64_t k_per_slice, float* __restrict__ logits) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, kq = lane & 3;
+  const int wm = warp & 1, wn = warp >> 1;
+  const int64_t t0 = (int64_t)blockIdx.x * RM_TM + 16 * wm;
+  const int64_t e0 = (int64_t)blockIdx.y * RM_TE + 32 * wn;
+  const int64_t k_lo = (int64_t)blockIdx.z * k_per_slice;
+  const int64_t k_hi = min(k_lo + k_per_slice, H);
+  const bool bf = is_bf16 != 0;
+
+  const int64_t ra = t0 + g, rb = t0 + g + 8;
+  const bool ra_ok = ra < T, rb_ok = rb < T;
+  const uint16_t* xa = x + (size_t)(ra_ok ? ra : 0) * H + 8 * kq;
+  const uint16_t* xb = x + (size_t)(rb_ok ? rb : 0) * H + 8 * kq;
+  const uint16_t* wp[4];
+  bool w_ok[4];
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    const int64_t e = e0 + 8 * n + g;
+    w_ok[n] = e < E;
+    wp[n] = w + (size_t)(w_ok[n] ? e : 0) * H + 8 * kq;
+  }
+
+  float master[4][4], part[4][4];
+#pragma unroll
+  for (int n = 0; n < 4; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { master[n][i] = 0.0f; part[n][i] = 0.0f; }
+
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  int in_chunk = 0;
+  for (int64_t k = k_lo; k < k_hi; k += 32) {
+    const uint4 va = ra_ok ? __ldg(reinterpret_cast<const uint4*>(xa + k)) : zero4;
+    const uint4 vb = rb_ok ? __ldg(reinterpret_cast<const uint4*>(xb + k)) : zero4;
+    uint4 vw[4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) vw[n] = w_ok[n] ? __ldg(reinterpret_cast<const uint4*>(wp[n] + k)) : zero4;
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      mma16816(part[n], va.x, vb.x, va.y, vb.y, vw[n].x, vw[n].y, bf);
+      mma16816(part[n], va.z, vb.z, va.w, vb.w, vw[n].z, vw[n].w, bf);
+    }
+    if (++in_chunk == 4) {          // 128 k summed in the tensor core: fold into the fp32 master
+      in_chunk = 0;
+#pragma unroll
+      for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { master[n][i] += part[n][i]; part[n][i] = 0.0f; }
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < 4; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) master[n][i] += part[n][i];
+
+  float* dst = logits + (size_t)blockIdx.z * T * E;
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    const int64_t e = e0 + 8 * n + 2 * kq;
+    if (ra_ok) {
+      if (e < E) dst[ra * E + e] = master[n][0];
+      if (e + 1 < E) dst[ra * E + e + 1] = master[n][1];
+    }
+    if (rb_ok) {
+      if (e < E) dst[rb * E + e] = master[n][2];
+      if (e + 1 < E) dst[rb * E + e + 1] = master[n][3];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Skinny logits (few tokens): one CTA per expert, each warp takes blocks of 8 tokens; the lanes
 // split H, partial sums meet in a shuffle tree.
 __global__ void __launch_bounds__(128)
@@ -292,7 +385,14 @@ extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_d
     slices = router_slices(T, H, E);
     int64_t k_per_slice = ((H + slices - 1) / slices + R_KC - 1) / R_KC * R_KC;
     dim3 grid((unsigned)((T + R_TM - 1) / R_TM), (unsigned)((E + R_TE - 1) / R_TE), (unsigned)slices);
-    router_logits_tiled<<<grid, R_THREADS, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, k_per_slice, vec_ok, logits_ws);
+    if (x_dtype == w_dtype && x_dtype != MQ_F32 && vec_ok && H % 32 == 0) {
+      // same tile shape as the SIMT kernel (32 tokens x 128 experts), so the grid and slices carry over
+      k_per_slice = (k_per_slice + 127) / 128 * 128;
+      router_logits_mma<<<grid, RM_THREADS, 0, st>>>(reinterpret_cast<const uint16_t*>(x),
+          reinterpret_cast<const uint16_t*>(w), x_dtype == MQ_BF16, T, H, E, k_per_slice, logits_ws);
+    } else {
+      router_logits_tiled<<<grid, R_THREADS, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, k_per_slice, vec_ok, logits_ws);
+    }
   }
   int rc = check_launch();
   if (rc != MQ_OK) return rc;

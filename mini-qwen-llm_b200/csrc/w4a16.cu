@@ -15,14 +15,27 @@
 //   * a group's partial sum is scaled once by s (fp32) when the group ends, so the dequantised
 //     weight is never rounded to bf16: sum_k x*(q-z) is exact-integer weights in the tensor core,
 //     times s in fp32, which is the reference's all-fp32 formula up to summation order;
-//   * the 4 warps of a CTA split K; their partial sums meet in shared memory in a fixed order.
+//   * the 4 warps of a CTA split K; their partial sums meet in shared memory in a fixed order;
+//   * every lane streams its own 16-byte pieces (weights and activations) through an 8-deep ring of
+//     cp.async copies in shared memory: a lane only ever reads what it copied itself, so the ring
+//     needs no barrier and no bank-conflict care, and 12 KB per warp are in flight while it computes.
 #include "common.cuh"
 
 namespace mq {
 namespace {
 
 constexpr int W4_WARPS = 4;
-constexpr int W4_NB = 2;          // row blocks of 8 handled per pass over the weights
+constexpr int W4_NB = 1;          // row blocks of 8 handled per pass over the weights
+constexpr int W4_DEPTH = 8;       // k-steps (32 k each) in flight per warp
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r;
@@ -120,6 +133,9 @@ w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
                      const int32_t* __restrict__ offsets, int period, int N, int Kd, int group,
                      __nv_bfloat16* __restrict__ out) {
   constexpr int NP = SWIGLU ? 2 : 1;
+  constexpr int SLOT = NP + W4_NB;                  // 16-byte pieces per lane and k-step
+  extern __shared__ uint4 ring_raw[];               // [W4_WARPS][W4_DEPTH][SLOT][32] 16-byte pieces
+  uint4(*ring)[W4_DEPTH][SLOT][32] = reinterpret_cast<uint4(*)[W4_DEPTH][SLOT][32]>(ring_raw);
   __shared__ float red[W4_WARPS][NP][W4_NB * 8][32];
 
   const int e = blockIdx.y;
@@ -159,24 +175,43 @@ w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
       xrow[tb] = x + (size_t)(row_lo + (row_ok[tb] ? r : 0)) * Kd;
     }
 
-    int cur_group = -1;
-    uint4 wnext[NP];
+    // one commit group per k-step, empty when there is nothing left to fetch, so that
+    // "all but the newest DEPTH-1 groups are complete" always means "this step has landed"
+    auto issue = [&](int s) {
+      if (s < s_hi) {
+        uint4(*slot)[32] = ring[warp][(s - s_lo) % W4_DEPTH];
+        if (col_ok) {
 #pragma unroll
-    for (int p = 0; p < NP; ++p) {
-      wnext[p] = make_uint4(0, 0, 0, 0);
-      if (col_ok && s_lo < s_hi)
-        wnext[p] = __ldg(reinterpret_cast<const uint4*>(proj[p].qw + qw_e + (size_t)(4 * s_lo + kq) * N + col0));
-    }
+          for (int p = 0; p < NP; ++p)
+            cp_async16(&slot[p][lane], proj[p].qw + qw_e + (size_t)(4 * s + kq) * N + col0);
+        }
+#pragma unroll
+        for (int tb = 0; tb < W4_NB; ++tb)
+          if (row_ok[tb]) cp_async16(&slot[NP + tb][lane], xrow[tb] + 32 * s + 8 * kq);
+      }
+      cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < W4_DEPTH; ++i) issue(s_lo + i);
 
+    int cur_group = -1;
     for (int s = s_lo; s < s_hi; ++s) {
+      cp_async_wait<W4_DEPTH - 1>();
+      uint4(*slot)[32] = ring[warp][(s - s_lo) % W4_DEPTH];
       uint4 wcur[NP];
 #pragma unroll
-      for (int p = 0; p < NP; ++p) wcur[p] = wnext[p];
-      if (s + 1 < s_hi && col_ok) {
+      for (int p = 0; p < NP; ++p) wcur[p] = col_ok ? slot[p][lane] : make_uint4(0, 0, 0, 0);
+      // activations: 8 consecutive k of row g (per row block), permuted to the nibble-pair order
+      uint32_t bfrag[W4_NB][4];
 #pragma unroll
-        for (int p = 0; p < NP; ++p)
-          wnext[p] = __ldg(reinterpret_cast<const uint4*>(proj[p].qw + qw_e + (size_t)(4 * (s + 1) + kq) * N + col0));
+      for (int tb = 0; tb < W4_NB; ++tb) {
+        const uint4 xv = row_ok[tb] ? slot[NP + tb][lane] : make_uint4(0, 0, 0, 0);
+        bfrag[tb][0] = prmt(xv.x, xv.z, 0x5410);  // {x0, x4}
+        bfrag[tb][1] = prmt(xv.x, xv.z, 0x7632);  // {x1, x5}
+        bfrag[tb][2] = prmt(xv.y, xv.w, 0x5410);  // {x2, x6}
+        bfrag[tb][3] = prmt(xv.y, xv.w, 0x7632);  // {x3, x7}
       }
+      issue(s + W4_DEPTH);               // refill the slot just read
       const int gi = s / steps_per_group;
       if (gi != cur_group) {
 #pragma unroll
@@ -186,20 +221,10 @@ w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
         }
         cur_group = gi;
       }
-      // activations: 8 consecutive k of row g (per row block), permuted to the nibble-pair order
-      uint32_t bfrag[W4_NB][4];
-#pragma unroll
-      for (int tb = 0; tb < W4_NB; ++tb) {
-        uint4 xv = make_uint4(0, 0, 0, 0);
-        if (row_ok[tb]) xv = __ldg(reinterpret_cast<const uint4*>(xrow[tb] + 32 * s + 8 * kq));
-        bfrag[tb][0] = prmt(xv.x, xv.z, 0x5410);  // {x0, x4}
-        bfrag[tb][1] = prmt(xv.x, xv.z, 0x7632);  // {x1, x5}
-        bfrag[tb][2] = prmt(xv.y, xv.w, 0x5410);  // {x2, x6}
-        bfrag[tb][3] = prmt(xv.y, xv.w, 0x7632);  // {x3, x7}
-      }
 #pragma unroll
       for (int p = 0; p < NP; ++p) step_mma(acc[p], wcur[p], bfrag);
     }
+    cp_async_wait<0>();
 #pragma unroll
     for (int p = 0; p < NP; ++p) acc_flush(acc[p]);
 
@@ -260,12 +285,16 @@ int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* o
   if (!aligned16(x) || !aligned16(p0.qw) || !aligned16(p0.sc) || !aligned16(out)) return MQ_ERR_INVALID_ARGUMENT;
   if (swiglu && (!aligned16(p1.qw) || !aligned16(p1.sc))) return MQ_ERR_INVALID_ARGUMENT;
   dim3 grid((unsigned)((N + 31) / 32), (unsigned)E);
-  if (swiglu)
-    w4a16_grouped_kernel<true><<<grid, W4_WARPS * 32, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), p0, p1,
+  const int ring_bytes = W4_WARPS * W4_DEPTH * ((swiglu ? 2 : 1) + W4_NB) * 32 * 16;
+  if (swiglu) {
+    cudaFuncSetAttribute(w4a16_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes);
+    w4a16_grouped_kernel<true><<<grid, W4_WARPS * 32, ring_bytes, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), p0, p1,
         offsets, (int)period, (int)N, (int)Kd, (int)group, reinterpret_cast<__nv_bfloat16*>(out));
-  else
-    w4a16_grouped_kernel<false><<<grid, W4_WARPS * 32, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), p0, p0,
+  } else {
+    cudaFuncSetAttribute(w4a16_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes);
+    w4a16_grouped_kernel<false><<<grid, W4_WARPS * 32, ring_bytes, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), p0, p0,
         offsets, (int)period, (int)N, (int)Kd, (int)group, reinterpret_cast<__nv_bfloat16*>(out));
+  }
   return check_launch();
 }
 
