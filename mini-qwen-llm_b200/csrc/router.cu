@@ -343,14 +343,22 @@ void launch_topk(const float* logits, int slices, const float* bias, int64_t T, 
 
 namespace mq {
 namespace {
-// K slices for the tiled logits kernel: enough CTAs for two per SM, slices a multiple of 32 wide.
-int router_slices(int64_t T, int64_t H, int64_t E) {
-  if (T <= 64) return 1;
+// Batches up to this size use the one-warp-per-(expert, 8 tokens) kernel.
+constexpr int64_t R_SKINNY_MAX_T = 15;
+
+// True when the tensor-core logits kernel applies: both operands 16-bit of the same type, 16-byte rows.
+bool router_mma_ok(int x_dtype, int w_dtype, int64_t H) { return x_dtype == w_dtype && x_dtype != MQ_F32 && H % 32 == 0; }
+
+// K slices for the tiled logits kernels: enough CTAs for two per SM.  The tensor-core kernel takes
+// slices of at least 128 k (one accumulation chunk), the SIMT kernel of at least 256 k.
+int router_slices(int64_t T, int64_t H, int64_t E, bool mma) {
+  if (T <= R_SKINNY_MAX_T) return 1;
   const int64_t ctas = ((T + R_TM - 1) / R_TM) * ((E + R_TE - 1) / R_TE);
   int64_t s = (2 * 148 + ctas - 1) / ctas;
-  const int64_t max_s = (H + 255) / 256;          // keep at least 256 k per slice
+  const int64_t max_s = mma ? (H + 127) / 128 : (H + 255) / 256;
+  const int64_t cap = mma ? 16 : 8;
   if (s > max_s) s = max_s;
-  if (s > 8) s = 8;
+  if (s > cap) s = cap;
   if (s < 1) s = 1;
   return (int)s;
 }
@@ -359,7 +367,8 @@ int router_slices(int64_t T, int64_t H, int64_t E) {
 
 extern "C" size_t mq_router_workspace_bytes(int64_t T, int64_t H, int64_t E) {
   if (T <= 0 || E <= 0 || H <= 0) return 16;
-  return (size_t)mq::router_slices(T, H, E) * (size_t)T * (size_t)E * sizeof(float);
+  // the dtype is not known here: size for the larger of the two slice counts
+  return (size_t)mq::router_slices(T, H, E, H % 32 == 0) * (size_t)T * (size_t)E * sizeof(float);
 }
 
 extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
@@ -379,15 +388,16 @@ extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_d
   int vec_ok = (H % 8 == 0) && aligned16(x) && aligned16(w);
 
   int slices = 1;
-  if (T <= 64) {
+  if (T <= R_SKINNY_MAX_T) {
     router_logits_skinny<<<(unsigned)E, 128, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, vec_ok, logits_ws);
   } else {
-    slices = router_slices(T, H, E);
-    int64_t k_per_slice = ((H + slices - 1) / slices + R_KC - 1) / R_KC * R_KC;
+    const bool mma = vec_ok && router_mma_ok(x_dtype, w_dtype, H);
+    slices = router_slices(T, H, E, mma);
+    int64_t k_per_slice = (H + slices - 1) / slices;
+    k_per_slice = mma ? (k_per_slice + 127) / 128 * 128 : (k_per_slice + R_KC - 1) / R_KC * R_KC;
     dim3 grid((unsigned)((T + R_TM - 1) / R_TM), (unsigned)((E + R_TE - 1) / R_TE), (unsigned)slices);
-    if (x_dtype == w_dtype && x_dtype != MQ_F32 && vec_ok && H % 32 == 0) {
-      // same tile shape as the SIMT kernel (32 tokens x 128 experts), so the grid and slices carry over
-      k_per_slice = (k_per_slice + 127) / 128 * 128;
+    if (mma) {
+      // same tile shape as the SIMT kernel (32 tokens x 128 experts), so the grid carries over
       router_logits_mma<<<grid, RM_THREADS, 0, st>>>(reinterpret_cast<const uint16_t*>(x),
           reinterpret_cast<const uint16_t*>(w), x_dtype == MQ_BF16, T, H, E, k_per_slice, logits_ws);
     } else {

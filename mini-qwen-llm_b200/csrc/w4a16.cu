@@ -2,31 +2,36 @@
 // Format and arithmetic follow mini_qwen/kernels/w4a16_gemm.py:8-15 and
 // tests/test_w4a16_gemm.py:19-44 of the reference: W[k,n] = (q[k,n] - z[k/g,n]) * s[k/g,n].
 //
-// The work is a stream over the packed weights (HBM-bound), so the kernel is organised around
-// the weight words, not around the output tile:
-//   * a lane reads one 128-bit vector = 4 adjacent columns x 8 consecutive k of packed int4,
-//     straight in the checkpoint layout [K/8, N] (8 lanes cover a full 128-byte line);
-//   * nibbles become bf16 in registers: (w >> 4p) & 0x000F000F | 0x43004300 is the bf16 pair
-//     {128+q[p], 128+q[p+4]}, and one packed subtract of {128+z, 128+z} leaves the exact
-//     integers q-z;
-//   * those integers are the A operand (16 columns x 16 k) of mma.sync.m16n8k16 with the
-//     activations as the 8-wide B operand ("swap-AB": rows of x are the narrow dimension), the
-//     k order inside a word being permuted identically on both operands;
-//   * a group's partial sum is scaled once by s (fp32) when the group ends, so the dequantised
-//     weight is never rounded to bf16: sum_k x*(q-z) is exact-integer weights in the tensor core,
-//     times s in fp32, which is the reference's all-fp32 formula up to summation order;
-//   * the 4 warps of a CTA split K; their partial sums meet in shared memory in a fixed order;
-//   * every lane streams its own 16-byte pieces (weights and activations) through an 8-deep ring of
-//     cp.async copies in shared memory: a lane only ever reads what it copied itself, so the ring
-//     needs no barrier and no bank-conflict care, and 12 KB per warp are in flight while it computes.
+// The work is a stream over the packed weights.  At 6.5 TB/s a B200 delivers 46 int4 weights per SM
+// and clock, which leaves under three lane-instructions per weight: the kernel is organised to
+// spend as few instructions per weight as possible, not around an output tile.
+//   * A lane reads one 128-bit vector = 4 adjacent columns x 8 consecutive k of packed int4,
+//     straight in the checkpoint layout [K/8, N] (8 lanes cover a full 128-byte line).
+//   * Nibbles become bf16 with ONE logic op per pair: (w >> 4p) & 0x000F000F | 0x43004300 is the
+//     bf16 pair {128+q[p], 128+q[p+4]}.  The zero point is not subtracted per weight: with
+//     xs = sum_k x[k] over the group (obtained from one extra MMA against a tile of ones),
+//        sum_k x[k] * (q[k] - z) = sum_k x[k] * (128 + q[k])  -  (128 + z) * xs ,
+//     and the right-hand side is evaluated once per group and column in fp32.
+//   * The biased integers are the A operand (16 columns x 16 k) of mma.sync.m16n8k16 with the
+//     activations as the 8-wide B operand ("swap-AB": rows of x are the narrow dimension); the k
+//     order inside a word is permuted identically on both operands.
+//   * A group's sum is scaled once by s (fp32) when the group ends, so the dequantised weight is
+//     never rounded to bf16.
+//   * Each warp streams TWO weight tiles against the same activations (gate and up of the same
+//     32 columns for SwiGLU, two adjacent 32-column tiles otherwise); the 4 warps of a CTA split K
+//     and their partial sums meet in shared memory in a fixed order.
+//   * Every lane moves its own 16-byte pieces (weights and activations) through an 8-deep ring of
+//     cp.async copies in shared memory: a lane only reads what it copied itself, so the ring needs
+//     no barrier and has no bank conflicts, and 12 KB per warp are in flight while it computes.
 #include "common.cuh"
 
 namespace mq {
 namespace {
 
 constexpr int W4_WARPS = 4;
-constexpr int W4_NB = 1;          // row blocks of 8 handled per pass over the weights
-constexpr int W4_DEPTH = 8;       // k-steps (32 k each) in flight per warp
+constexpr int W4_DEPTH = 8;       // k-steps (32 k each) in flight per warp (power of two)
+constexpr int W4_NS = 2;          // weight streams per warp
+constexpr uint32_t BF16_ONES = 0x3F803F80u;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc)
@@ -43,12 +48,11 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   return r;
 }
 
-// pair p of word w -> bf16x2 {q[p] - z, q[p+4] - z}
-__device__ __forceinline__ uint32_t dequant_pair(uint32_t w, int p, uint32_t zb) {
+// pair p of word w -> bf16x2 {128 + q[p], 128 + q[p+4]}
+__device__ __forceinline__ uint32_t biased_pair(uint32_t w, int p) {
   uint32_t v;
   asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(w >> (4 * p)), "r"(0x000F000Fu), "r"(0x43004300u));
-  __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), *reinterpret_cast<__nv_bfloat162*>(&zb));
-  return *reinterpret_cast<uint32_t*>(&d);
+  return v;
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -65,213 +69,299 @@ struct W4Proj {
   const int32_t* qz;        // [E, Kd/g, N/8]
 };
 
-// Accumulators of one projection for one lane: 4 columns x 2 rows per row block.
-struct W4Acc {
-  float master[W4_NB][2][4];
-  float grp[W4_NB][2][4];
+// One weight stream of a lane: 4 columns x (rows 2kq, 2kq+1) in two MMA fragments.
+struct W4Stream {
+  float master[2][4];
+  float grp[2][4];
   float scale[4];
-  uint32_t zb[4];
+  float zoff[4];            // 128 + zero point of the current group
 };
 
-__device__ __forceinline__ void acc_init(W4Acc& a) {
+__device__ __forceinline__ void stream_init(W4Stream& a) {
 #pragma unroll
-  for (int tb = 0; tb < W4_NB; ++tb)
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int m = 0; m < 2; ++m)
+    for (int i = 0; i < 4; ++i) { a.master[m][i] = 0.0f; a.grp[m][i] = 0.0f; }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { a.master[tb][m][i] = 0.0f; a.grp[tb][m][i] = 0.0f; }
-#pragma unroll
-  for (int c = 0; c < 4; ++c) { a.scale[c] = 0.0f; a.zb[c] = 0x43004300u; }
+  for (int c = 0; c < 4; ++c) { a.scale[c] = 0.0f; a.zoff[c] = 0.0f; }
 }
 
-__device__ __forceinline__ void acc_flush(W4Acc& a) {
+// End of a group: master += s * (sum_k x*(128+q) - (128+z) * sum_k x), then restart the group sums.
+__device__ __forceinline__ void stream_flush(W4Stream& a, const float (&xs)[4]) {
 #pragma unroll
-  for (int tb = 0; tb < W4_NB; ++tb)
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int m = 0; m < 2; ++m)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        a.master[tb][m][i] = fmaf(a.scale[2 * m + (i >> 1)], a.grp[tb][m][i], a.master[tb][m][i]);
-        a.grp[tb][m][i] = 0.0f;
-      }
+    for (int i = 0; i < 4; ++i) {
+      const int col = 2 * m + (i >> 1);
+      const float t = fmaf(-a.zoff[col], xs[i & 1], a.grp[m][i]);
+      a.master[m][i] = fmaf(a.scale[col], t, a.master[m][i]);
+      a.grp[m][i] = 0.0f;
+    }
 }
 
-__device__ __forceinline__ void load_group(W4Acc& a, const W4Proj& p, size_t sc_row, size_t qz_row, int col0) {
-  uint2 s = __ldg(reinterpret_cast<const uint2*>(p.sc + sc_row + col0));
-  a.scale[0] = __uint_as_float(s.x << 16);
-  a.scale[1] = __uint_as_float(s.x & 0xffff0000u);
-  a.scale[2] = __uint_as_float(s.y << 16);
-  a.scale[3] = __uint_as_float(s.y & 0xffff0000u);
-  uint32_t zw = (uint32_t)__ldg(p.qz + qz_row + (col0 >> 3));
-  zw >>= (col0 & 7) * 4;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) a.zb[c] = (0x4300u | ((zw >> (4 * c)) & 0xFu)) * 0x00010001u;
-}
-
-__device__ __forceinline__ void step_mma(W4Acc& a, const uint4& wv, const uint32_t (&bfrag)[W4_NB][4]) {
+__device__ __forceinline__ void stream_step(W4Stream& a, const uint4& wv, const uint32_t (&b)[4]) {
   const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
   uint32_t d[4][4];
 #pragma unroll
   for (int c = 0; c < 4; ++c)
 #pragma unroll
-    for (int p = 0; p < 4; ++p) d[c][p] = dequant_pair(w[c], p, a.zb[c]);
+    for (int p = 0; p < 4; ++p) d[c][p] = biased_pair(w[c], p);
 #pragma unroll
-  for (int tb = 0; tb < W4_NB; ++tb) {
-#pragma unroll
-    for (int m = 0; m < 2; ++m) {
-      mma_bf16_16816(a.grp[tb][m], d[2 * m][0], d[2 * m + 1][0], d[2 * m][1], d[2 * m + 1][1],
-                     bfrag[tb][0], bfrag[tb][1]);
-      mma_bf16_16816(a.grp[tb][m], d[2 * m][2], d[2 * m + 1][2], d[2 * m][3], d[2 * m + 1][3],
-                     bfrag[tb][2], bfrag[tb][3]);
-    }
+  for (int m = 0; m < 2; ++m) {
+    mma_bf16_16816(a.grp[m], d[2 * m][0], d[2 * m + 1][0], d[2 * m][1], d[2 * m + 1][1], b[0], b[1]);
+    mma_bf16_16816(a.grp[m], d[2 * m][2], d[2 * m + 1][2], d[2 * m][3], d[2 * m + 1][3], b[2], b[3]);
   }
 }
 
-template <bool SWIGLU>
-__global__ void __launch_bounds__(W4_WARPS * 32)
-w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
-                     const int32_t* __restrict__ offsets, int period, int N, int Kd, int group,
-                     __nv_bfloat16* __restrict__ out) {
-  constexpr int NP = SWIGLU ? 2 : 1;
-  constexpr int SLOT = NP + W4_NB;                  // 16-byte pieces per lane and k-step
-  extern __shared__ uint4 ring_raw[];               // [W4_WARPS][W4_DEPTH][SLOT][32] 16-byte pieces
-  uint4(*ring)[W4_DEPTH][SLOT][32] = reinterpret_cast<uint4(*)[W4_DEPTH][SLOT][32]>(ring_raw);
-  __shared__ float red[W4_WARPS][NP][W4_NB * 8][32];
+// Raw scale / zero-point words of one group for a lane's 4 columns (fetched one group ahead).
+struct W4Meta {
+  uint2 s;
+  uint32_t z;
+};
 
-  const int e = blockIdx.y;
+__device__ __forceinline__ W4Meta meta_fetch(const __nv_bfloat16* sc, const int32_t* qz, int col) {
+  W4Meta m;
+  m.s = __ldg(reinterpret_cast<const uint2*>(sc + col));
+  m.z = (uint32_t)__ldg(qz + (col >> 3)) >> ((col & 7) * 4);
+  return m;
+}
+
+__device__ __forceinline__ void stream_set_group(W4Stream& a, const W4Meta& m) {
+  a.scale[0] = __uint_as_float(m.s.x << 16);
+  a.scale[1] = __uint_as_float(m.s.x & 0xffff0000u);
+  a.scale[2] = __uint_as_float(m.s.y << 16);
+  a.scale[3] = __uint_as_float(m.s.y & 0xffff0000u);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) a.zoff[c] = (float)(128u + ((m.z >> (4 * c)) & 0xFu));
+}
+
+// The y-th non-empty group of rows (y = blockIdx.y), found with ballots over the offsets; -1 if
+// there are fewer.  Lets a decode launch size its grid by the slot count instead of the expert count.
+__device__ int nth_nonempty(const int32_t* offsets, int E, int y, int* s_e) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int found = -1, seen = 0;
+    for (int e0 = 0; e0 < E && found < 0; e0 += 32) {
+      const int e = e0 + lane;
+      const bool ne = e < E && offsets[e + 1] > offsets[e];
+      const unsigned m = __ballot_sync(0xffffffffu, ne);
+      const int c = __popc(m);
+      if (y < seen + c) {
+        unsigned mm = m;
+        for (int i = 0; i < y - seen; ++i) mm &= mm - 1;     // drop the lowest set bits
+        found = e0 + __ffs(mm) - 1;
+      }
+      seen += c;
+    }
+    if (lane == 0) *s_e = found;
+  }
+  __syncthreads();
+  return *s_e;
+}
+
+// KSPLIT = 4: the CTA's warps split K over one column tile (few rows in total: more CTAs per byte).
+// KSPLIT = 1: every warp owns its own column tile and runs the whole K (long streams, no exchange).
+template <bool SWIGLU, int KSPLIT>
+__global__ void __launch_bounds__(W4_WARPS * 32, 4)
+w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
+                     const int32_t* __restrict__ offsets, int E, int period, int N, int Kd, int group,
+                     int compact, __nv_bfloat16* __restrict__ out) {
+  // SWIGLU: the two streams of a warp are the gate and up projections of the same 32 columns.
+  // Plain: the two streams are adjacent 32-column tiles (64 columns per warp).
+  constexpr int SLOT = W4_NS + 1;                    // 16-byte pieces per lane and k-step: 2 weights + x
+  __shared__ uint4 ring[W4_WARPS][W4_DEPTH][SLOT][32];
+
+  int e = (int)blockIdx.y;
+  if (compact) {
+    // the first word of the (still unused) ring carries the expert index from warp 0 to the others
+    e = nth_nonempty(offsets, E, blockIdx.y, reinterpret_cast<int*>(&ring[0][0][0][0]));
+    __syncthreads();                     // everyone has read it before any copy lands in the ring
+  }
+  if (e < 0) return;
   const int row_lo = offsets[e];
   const int rows = offsets[e + 1] - row_lo;
   if (rows <= 0) return;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, kq = lane & 3;
-  const int col0 = blockIdx.x * 32 + 4 * g;
-  const bool col_ok = col0 < N;
+  const int cols_per_tile = SWIGLU ? 32 : 64;
+  const int tile = KSPLIT == 1 ? (int)blockIdx.x * W4_WARPS + warp : (int)blockIdx.x;
+  const int col[W4_NS] = {tile * cols_per_tile + 4 * g, tile * cols_per_tile + (SWIGLU ? 0 : 32) + 4 * g};
+  const bool col_ok[W4_NS] = {col[0] < N, col[1] < N};
+  // lanes past the last column (or row) stream a valid neighbour instead and simply do not store:
+  // the inner loop then carries no per-lane selects
+  const int colc[W4_NS] = {col_ok[0] ? col[0] : N - 4, col_ok[1] ? col[1] : N - 4};
 
   const int steps_total = Kd / 32;
-  const int spw = (steps_total + W4_WARPS - 1) / W4_WARPS;
-  const int s_lo = warp * spw;
+  const int spw = KSPLIT == 1 ? steps_total : (steps_total + W4_WARPS - 1) / W4_WARPS;
+  const int s_lo = KSPLIT == 1 ? 0 : warp * spw;
   const int s_hi = min(s_lo + spw, steps_total);
-  const int steps_per_group = group / 32;
+  const int spg = group / 32;           // k-steps per quantisation group
   const int G = Kd / group;
 
-  const int we = e % period;            // weight set of this group
-  const size_t qw_e = (size_t)we * (Kd / 8) * N;
-  const size_t sc_e = (size_t)we * G * N;
-  const size_t qz_e = (size_t)we * G * (N / 8);
-  const W4Proj proj[2] = {p0, p1};
+  const int we = e % period;            // weight set of this group of rows
+  const W4Proj proj[W4_NS] = {p0, SWIGLU ? p1 : p0};
+  const int32_t* qw[W4_NS];
+  const __nv_bfloat16* sc[W4_NS];
+  const int32_t* qz[W4_NS];
+#pragma unroll
+  for (int j = 0; j < W4_NS; ++j) {
+    qw[j] = proj[j].qw + (size_t)we * (Kd / 8) * N + (size_t)kq * N + colc[j];
+    sc[j] = proj[j].sc + (size_t)we * G * N;
+    qz[j] = proj[j].qz + (size_t)we * G * (N / 8);
+  }
+  uint4* const ring_lane = &ring[warp][0][0][lane];
+  constexpr int SLOT_STRIDE = SLOT * 32;             // uint4 elements between two ring slots
 
-  for (int r0 = 0; r0 < rows; r0 += 8 * W4_NB) {
-    W4Acc acc[NP];
+  for (int r0 = 0; r0 < rows; r0 += 8) {
+    W4Stream st[W4_NS];
 #pragma unroll
-    for (int p = 0; p < NP; ++p) acc_init(acc[p]);
+    for (int j = 0; j < W4_NS; ++j) stream_init(st[j]);
+    float xs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
-    const __nv_bfloat16* xrow[W4_NB];
-    bool row_ok[W4_NB];
-#pragma unroll
-    for (int tb = 0; tb < W4_NB; ++tb) {
-      int r = r0 + 8 * tb + g;
-      row_ok[tb] = r < rows;
-      xrow[tb] = x + (size_t)(row_lo + (row_ok[tb] ? r : 0)) * Kd;
-    }
+    const int rowc = r0 + g < rows ? r0 + g : 0;
+    const __nv_bfloat16* xrow = x + (size_t)(row_lo + rowc) * Kd + 8 * kq;
 
-    // one commit group per k-step, empty when there is nothing left to fetch, so that
-    // "all but the newest DEPTH-1 groups are complete" always means "this step has landed"
-    auto issue = [&](int s) {
-      if (s < s_hi) {
-        uint4(*slot)[32] = ring[warp][(s - s_lo) % W4_DEPTH];
-        if (col_ok) {
+    // Prologue: DEPTH steps in flight.  One commit group per k-step, empty when there is nothing
+    // left to fetch, so "all but the newest DEPTH-1 groups are complete" means "this step has landed".
+    uint32_t w_off = (uint32_t)(4 * s_lo) * (uint32_t)N;     // element offset of the next step to fetch
+    uint32_t x_off = 32u * (uint32_t)s_lo;
+    int fetch = s_lo;
 #pragma unroll
-          for (int p = 0; p < NP; ++p)
-            cp_async16(&slot[p][lane], proj[p].qw + qw_e + (size_t)(4 * s + kq) * N + col0);
-        }
-#pragma unroll
-        for (int tb = 0; tb < W4_NB; ++tb)
-          if (row_ok[tb]) cp_async16(&slot[NP + tb][lane], xrow[tb] + 32 * s + 8 * kq);
+    for (int i = 0; i < W4_DEPTH; ++i) {
+      if (fetch < s_hi) {
+        uint4* sl = ring_lane + i * SLOT_STRIDE;
+        cp_async16(sl, qw[0] + w_off);
+        cp_async16(sl + 32, qw[1] + w_off);
+        cp_async16(sl + 64, xrow + x_off);
       }
       cp_async_commit();
-    };
-#pragma unroll
-    for (int i = 0; i < W4_DEPTH; ++i) issue(s_lo + i);
+      w_off += 4u * (uint32_t)N;
+      x_off += 32u;
+      ++fetch;
+    }
 
-    int cur_group = -1;
+    // scales and zero points travel one group ahead of their use
+    int gi = s_lo / spg;
+    int left = spg - (s_lo - gi * spg);                // steps until the current group ends
+    W4Meta next[W4_NS];
+#pragma unroll
+    for (int j = 0; j < W4_NS; ++j) {
+      const W4Meta cur = meta_fetch(sc[j] + (size_t)gi * N, qz[j] + (size_t)gi * (N / 8), colc[j]);
+      stream_set_group(st[j], cur);
+      next[j] = cur;
+      if (gi + 1 < G) next[j] = meta_fetch(sc[j] + (size_t)(gi + 1) * N, qz[j] + (size_t)(gi + 1) * (N / 8), colc[j]);
+    }
+
+    int slot_idx = 0;
     for (int s = s_lo; s < s_hi; ++s) {
       cp_async_wait<W4_DEPTH - 1>();
-      uint4(*slot)[32] = ring[warp][(s - s_lo) % W4_DEPTH];
-      uint4 wcur[NP];
-#pragma unroll
-      for (int p = 0; p < NP; ++p) wcur[p] = col_ok ? slot[p][lane] : make_uint4(0, 0, 0, 0);
-      // activations: 8 consecutive k of row g (per row block), permuted to the nibble-pair order
-      uint32_t bfrag[W4_NB][4];
-#pragma unroll
-      for (int tb = 0; tb < W4_NB; ++tb) {
-        const uint4 xv = row_ok[tb] ? slot[NP + tb][lane] : make_uint4(0, 0, 0, 0);
-        bfrag[tb][0] = prmt(xv.x, xv.z, 0x5410);  // {x0, x4}
-        bfrag[tb][1] = prmt(xv.x, xv.z, 0x7632);  // {x1, x5}
-        bfrag[tb][2] = prmt(xv.y, xv.w, 0x5410);  // {x2, x6}
-        bfrag[tb][3] = prmt(xv.y, xv.w, 0x7632);  // {x3, x7}
+      uint4* sl = ring_lane + slot_idx * SLOT_STRIDE;
+      const uint4 wv0 = sl[0];
+      const uint4 wv1 = sl[32];
+      const uint4 xv = sl[64];
+      if (fetch < s_hi) {                              // refill the slot just read
+        cp_async16(sl, qw[0] + w_off);
+        cp_async16(sl + 32, qw[1] + w_off);
+        cp_async16(sl + 64, xrow + x_off);
       }
-      issue(s + W4_DEPTH);               // refill the slot just read
-      const int gi = s / steps_per_group;
-      if (gi != cur_group) {
+      cp_async_commit();
+      w_off += 4u * (uint32_t)N;
+      x_off += 32u;
+      ++fetch;
+      slot_idx = (slot_idx + 1) & (W4_DEPTH - 1);
+      // activations: 8 consecutive k of row g, permuted to the nibble-pair order
+      const uint32_t b[4] = {prmt(xv.x, xv.z, 0x5410),   // {x0, x4}
+                             prmt(xv.x, xv.z, 0x7632),   // {x1, x5}
+                             prmt(xv.y, xv.w, 0x5410),   // {x2, x6}
+                             prmt(xv.y, xv.w, 0x7632)};  // {x3, x7}
+      mma_bf16_16816(xs, BF16_ONES, BF16_ONES, BF16_ONES, BF16_ONES, b[0], b[1]);
+      mma_bf16_16816(xs, BF16_ONES, BF16_ONES, BF16_ONES, BF16_ONES, b[2], b[3]);
+      stream_step(st[0], wv0, b);
+      stream_step(st[1], wv1, b);
+      if (--left == 0) {                               // group boundary
+        ++gi;
 #pragma unroll
-        for (int p = 0; p < NP; ++p) {
-          acc_flush(acc[p]);
-          if (col_ok) load_group(acc[p], proj[p], sc_e + (size_t)gi * N, qz_e + (size_t)gi * (N / 8), col0);
+        for (int j = 0; j < W4_NS; ++j) {
+          stream_flush(st[j], xs);
+          stream_set_group(st[j], next[j]);
+          if (gi + 1 < G) next[j] = meta_fetch(sc[j] + (size_t)(gi + 1) * N, qz[j] + (size_t)(gi + 1) * (N / 8), colc[j]);
         }
-        cur_group = gi;
+        xs[0] = xs[1] = xs[2] = xs[3] = 0.0f;
+        left = spg;
       }
-#pragma unroll
-      for (int p = 0; p < NP; ++p) step_mma(acc[p], wcur[p], bfrag);
     }
     cp_async_wait<0>();
+    if (left != spg) {                                 // the K range ended inside a group
 #pragma unroll
-    for (int p = 0; p < NP; ++p) acc_flush(acc[p]);
+      for (int j = 0; j < W4_NS; ++j) stream_flush(st[j], xs);
+    }
 
-    // fixed-order reduction over the K split
+    if (KSPLIT > 1) {
+      // fixed-order reduction over the K split (the ring is idle now and doubles as the exchange buffer)
+      float(*red)[W4_NS][8][32] = reinterpret_cast<float(*)[W4_NS][8][32]>(&ring[0][0][0][0]);
+      __syncthreads();
 #pragma unroll
-    for (int p = 0; p < NP; ++p)
-#pragma unroll
-      for (int tb = 0; tb < W4_NB; ++tb)
-#pragma unroll
-        for (int m = 0; m < 2; ++m)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) red[warp][p][tb * 8 + m * 4 + i][lane] = acc[p].master[tb][m][i];
-    __syncthreads();
-    if (warp == 0 && col_ok) {
-#pragma unroll
-      for (int tb = 0; tb < W4_NB; ++tb)
+      for (int j = 0; j < W4_NS; ++j)
 #pragma unroll
         for (int m = 0; m < 2; ++m)
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {   // half selects the row 2kq + half
-            float v[NP][2];
+          for (int i = 0; i < 4; ++i) red[warp][j][m * 4 + i][lane] = st[j].master[m][i];
+      __syncthreads();
+      if (warp == 0) {
 #pragma unroll
-            for (int p = 0; p < NP; ++p)
+        for (int j = 0; j < W4_NS; ++j)
 #pragma unroll
-              for (int cc = 0; cc < 2; ++cc) {     // the two columns of this mma
-                const int idx = tb * 8 + m * 4 + cc * 2 + half;
-                float sum = red[0][p][idx][lane];
+          for (int m = 0; m < 2; ++m)
 #pragma unroll
-                for (int w = 1; w < W4_WARPS; ++w) sum += red[w][p][idx][lane];
-                v[p][cc] = sum;
+            for (int i = 0; i < 4; ++i) {
+              float sum = red[0][j][m * 4 + i][lane];
+#pragma unroll
+              for (int w = 1; w < W4_WARPS; ++w) sum += red[w][j][m * 4 + i][lane];
+              st[j].master[m][i] = sum;
+            }
+      }
+    }
+    if (KSPLIT == 1 || warp == 0) {
+      // fragment element i of mma m: column 2m + (i >> 1), row 2kq + (i & 1)
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = r0 + 2 * kq + half;
+          if (r < rows) {
+            __nv_bfloat16* orow = out + (size_t)(row_lo + r) * N + 2 * m;
+            if (SWIGLU) {
+              if (col_ok[0]) {
+                const float o0 = swiglu_rounded<__nv_bfloat16>(st[0].master[m][half], st[1].master[m][half]);
+                const float o1 = swiglu_rounded<__nv_bfloat16>(st[0].master[m][2 + half], st[1].master[m][2 + half]);
+                *reinterpret_cast<__nv_bfloat162*>(orow + col[0]) = __floats2bfloat162_rn(o0, o1);
               }
-            const int r = r0 + 8 * tb + 2 * kq + half;
-            if (r < rows) {
-              float o0, o1;
-              if (SWIGLU) {
-                o0 = swiglu_rounded<__nv_bfloat16>(v[0][0], v[NP - 1][0]);
-                o1 = swiglu_rounded<__nv_bfloat16>(v[0][1], v[NP - 1][1]);
-              } else {
-                o0 = v[0][0]; o1 = v[0][1];
-              }
-              __nv_bfloat162 o = __floats2bfloat162_rn(o0, o1);
-              *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(row_lo + r) * N + col0 + 2 * m) = o;
+            } else {
+#pragma unroll
+              for (int j = 0; j < W4_NS; ++j)
+                if (col_ok[j])
+                  *reinterpret_cast<__nv_bfloat162*>(orow + col[j]) =
+                      __floats2bfloat162_rn(st[j].master[m][half], st[j].master[m][2 + half]);
             }
           }
+        }
     }
-    __syncthreads();
+    if (KSPLIT > 1) __syncthreads();
   }
+}
+
+template <bool SWIGLU, int KSPLIT>
+void launch_w4_variant(const void* x, W4Proj p0, W4Proj p1, const int32_t* offsets, int64_t S, int64_t E,
+                       int64_t period, int64_t N, int64_t Kd, int64_t group, void* out, cudaStream_t st) {
+  const int cols_per_tile = SWIGLU ? 32 : 64;
+  const int cols_per_cta = KSPLIT == 1 ? cols_per_tile * W4_WARPS : cols_per_tile;
+  // with fewer slots than experts most experts are empty: index the grid by non-empty experts instead
+  const int compact = S < E;
+  dim3 grid((unsigned)((N + cols_per_cta - 1) / cols_per_cta), (unsigned)(compact ? S : E));
+  w4a16_grouped_kernel<SWIGLU, KSPLIT><<<grid, W4_WARPS * 32, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), p0, p1, offsets, (int)E, (int)period, (int)N, (int)Kd, (int)group,
+      compact, reinterpret_cast<__nv_bfloat16*>(out));
 }
 
 int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* offsets, int64_t S, int64_t E,
@@ -284,16 +374,15 @@ int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* o
   if (swiglu && (!p1.qw || !p1.sc || !p1.qz)) return MQ_ERR_INVALID_ARGUMENT;
   if (!aligned16(x) || !aligned16(p0.qw) || !aligned16(p0.sc) || !aligned16(out)) return MQ_ERR_INVALID_ARGUMENT;
   if (swiglu && (!aligned16(p1.qw) || !aligned16(p1.sc))) return MQ_ERR_INVALID_ARGUMENT;
-  dim3 grid((unsigned)((N + 31) / 32), (unsigned)E);
-  const int ring_bytes = W4_WARPS * W4_DEPTH * ((swiglu ? 2 : 1) + W4_NB) * 32 * 16;
+  // few rows in total (a handful of experts hit): split K across the warps of a CTA to get enough CTAs;
+  // otherwise every warp streams the whole K of its own column tile
+  const bool split = S <= 32;
   if (swiglu) {
-    cudaFuncSetAttribute(w4a16_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes);
-    w4a16_grouped_kernel<true><<<grid, W4_WARPS * 32, ring_bytes, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), p0, p1,
-        offsets, (int)period, (int)N, (int)Kd, (int)group, reinterpret_cast<__nv_bfloat16*>(out));
+    if (split) launch_w4_variant<true, 4>(x, p0, p1, offsets, S, E, period, N, Kd, group, out, st);
+    else launch_w4_variant<true, 1>(x, p0, p1, offsets, S, E, period, N, Kd, group, out, st);
   } else {
-    cudaFuncSetAttribute(w4a16_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes);
-    w4a16_grouped_kernel<false><<<grid, W4_WARPS * 32, ring_bytes, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), p0, p0,
-        offsets, (int)period, (int)N, (int)Kd, (int)group, reinterpret_cast<__nv_bfloat16*>(out));
+    if (split) launch_w4_variant<false, 4>(x, p0, p0, offsets, S, E, period, N, Kd, group, out, st);
+    else launch_w4_variant<false, 1>(x, p0, p0, offsets, S, E, period, N, Kd, group, out, st);
   }
   return check_launch();
 }
