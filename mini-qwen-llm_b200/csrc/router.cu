@@ -37,6 +37,21 @@ __device__ __forceinline__ void load8(const void* p, int dt, size_t i, float (&v
   }
 }
 
+// 8 packed 16-bit values -> fp32.
+__device__ __forceinline__ void unpack8_16bit(const uint4& r, bool bf16, float (&v)[8]) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (bf16) {
+      v[2 * j] = __uint_as_float(w[j] << 16);
+      v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    } else {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+      v[2 * j] = f.x; v[2 * j + 1] = f.y;
+    }
+  }
+}
+
 // 8 elements with bounds and alignment handled element by element (any H).
 __device__ __forceinline__ void load8_safe(const void* p, int dt, size_t row_base, int64_t k, int64_t H,
                                            bool vec_ok, float (&v)[8]) {
@@ -234,20 +249,43 @@ router_logits_skinny(const void* __restrict__ x, int xdt, const void* __restrict
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t e = blockIdx.x;
   const size_t w_row = (size_t)e * H;
+  const bool fast = vec_ok && xdt != MQ_F32 && wdt != MQ_F32;     // 16-bit operands, 16-byte pieces
   for (int64_t tb = (int64_t)warp * 8; tb < T; tb += 4 * 8) {
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-    for (int64_t k = (int64_t)lane * 8; k < H; k += 32 * 8) {
-      float wv[8];
-      load8_safe(w, wdt, w_row, k, H, vec_ok, wv);
+    if (fast) {
+      const uint16_t* wp = reinterpret_cast<const uint16_t*>(w) + w_row;
+      const uint16_t* xp = reinterpret_cast<const uint16_t*>(x);
+      for (int64_t k = (int64_t)lane * 8; k < H; k += 32 * 8) {
+        // all nine loads of the iteration are issued before the first use
+        const uint4 wr = __ldg(reinterpret_cast<const uint4*>(wp + k));
+        uint4 xr[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (tb + i < T) {
+        for (int i = 0; i < 8; ++i)
+          xr[i] = tb + i < T ? __ldg(reinterpret_cast<const uint4*>(xp + (size_t)(tb + i) * H + k)) : make_uint4(0, 0, 0, 0);
+        float wv[8];
+        unpack8_16bit(wr, wdt == MQ_BF16, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
           float xv[8];
-          load8_safe(x, xdt, (size_t)(tb + i) * H, k, H, vec_ok, xv);
+          unpack8_16bit(xr[i], xdt == MQ_BF16, xv);
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[i] = fmaf(xv[j], wv[j], acc[i]);
+        }
+      }
+    } else {
+      for (int64_t k = (int64_t)lane * 8; k < H; k += 32 * 8) {
+        float wv[8];
+        load8_safe(w, wdt, w_row, k, H, vec_ok, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (tb + i < T) {
+            float xv[8];
+            load8_safe(x, xdt, (size_t)(tb + i) * H, k, H, vec_ok, xv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[i] = fmaf(xv[j], wv[j], acc[i]);
+          }
         }
       }
     }
@@ -279,8 +317,12 @@ router_softmax_topk(const float* __restrict__ logits, int slices, const float* _
     int e = lane + 32 * j;
     float v = -INFINITY;
     if (e < E) {
-      v = logits[t * E + e];
-      for (int sl = 1; sl < slices; ++sl) v += logits[((size_t)sl * T + t) * E + e];   // fixed order
+      float part[16];                    // at most 16 K slices; loads first, then a fixed-order sum
+#pragma unroll
+      for (int sl = 0; sl < 16; ++sl) part[sl] = sl < slices ? logits[((size_t)sl * T + t) * E + e] : 0.0f;
+      v = part[0];
+#pragma unroll
+      for (int sl = 1; sl < 16; ++sl) if (sl < slices) v += part[sl];
       if (bias != nullptr) v += bias[e];
     }
     s[j] = v;
@@ -352,7 +394,7 @@ bool router_mma_ok(int x_dtype, int w_dtype, int64_t H) { return x_dtype == w_dt
 // K slices for the tiled logits kernels: enough CTAs for two per SM.  The tensor-core kernel takes
 // slices of at least 128 k (one accumulation chunk), the SIMT kernel of at least 256 k.
 int router_slices(int64_t T, int64_t H, int64_t E, bool mma) {
-  if (T <= R_SKINNY_MAX_T) return 1;
+  if (T <= R_SKINNY_MAX_T && !mma) return 1;
   const int64_t ctas = ((T + R_TM - 1) / R_TM) * ((E + R_TE - 1) / R_TE);
   int64_t s = (2 * 148 + ctas - 1) / ctas;
   const int64_t max_s = mma ? (H + 127) / 128 : (H + 255) / 256;
@@ -388,10 +430,10 @@ extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_d
   int vec_ok = (H % 8 == 0) && aligned16(x) && aligned16(w);
 
   int slices = 1;
-  if (T <= R_SKINNY_MAX_T) {
+  const bool mma = vec_ok && router_mma_ok(x_dtype, w_dtype, H);
+  if (T <= R_SKINNY_MAX_T && !mma) {
     router_logits_skinny<<<(unsigned)E, 128, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, vec_ok, logits_ws);
   } else {
-    const bool mma = vec_ok && router_mma_ok(x_dtype, w_dtype, H);
     slices = router_slices(T, H, E, mma);
     int64_t k_per_slice = (H + slices - 1) / slices;
     k_per_slice = mma ? (k_per_slice + 127) / 128 * 128 : (k_per_slice + R_KC - 1) / R_KC * R_KC;

@@ -23,13 +23,15 @@
 //   * Every lane moves its own 16-byte pieces (weights and activations) through an 8-deep ring of
 //     cp.async copies in shared memory: a lane only reads what it copied itself, so the ring needs
 //     no barrier and has no bank conflicts, and 12 KB per warp are in flight while it computes.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace mq {
 namespace {
 
 constexpr int W4_WARPS = 4;
-constexpr int W4_DEPTH = 8;       // k-steps (32 k each) in flight per warp (power of two)
+constexpr int W4_DEPTH = 4;       // k-steps (32 k each) in flight per warp (power of two)
 constexpr int W4_NS = 2;          // weight streams per warp
 constexpr uint32_t BF16_ONES = 0x3F803F80u;
 
@@ -376,7 +378,8 @@ int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* o
   if (swiglu && (!aligned16(p1.qw) || !aligned16(p1.sc))) return MQ_ERR_INVALID_ARGUMENT;
   // few rows in total (a handful of experts hit): split K across the warps of a CTA to get enough CTAs;
   // otherwise every warp streams the whole K of its own column tile
-  const bool split = S <= 32;
+  bool split = S <= 32;
+  if (const char* ov = getenv("MQ_W4_SPLIT")) split = ov[0] == '1';   // experiment switch
   if (swiglu) {
     if (split) launch_w4_variant<true, 4>(x, p0, p1, offsets, S, E, period, N, Kd, group, out, st);
     else launch_w4_variant<true, 1>(x, p0, p1, offsets, S, E, period, N, Kd, group, out, st);
