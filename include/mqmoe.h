@@ -42,6 +42,7 @@ typedef enum {
 
 /* bits of the device status word */
 #define MQ_DEV_WAIT_EXPIRED 1u   /* a bounded mbarrier wait gave up; the output is invalid */
+#define MQ_DEV_EP_OVERFLOW 2u    /* an expert-parallel receive buffer was too small; rows were dropped */
 
 int mq_version(void);
 const char* mq_status_string(int status);
@@ -168,6 +169,33 @@ int mq_w4a16_grouped_swiglu(const void* x,
                             const int32_t* offsets,
                             int64_t S, int64_t E, int64_t weight_period, int64_t I, int64_t H, int64_t group_size,
                             void* h, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Expert parallelism over peer memory (no counterpart in the reference, which is single-GPU).
+ * G ranks, rank r owns experts [r*E/G, (r+1)*E/G).  Every rank provides a receive buffer and an
+ * expert-output buffer of cap_rows rows that its peers can address (peer_*_ptrs: device array of
+ * G base addresses, entry r being the local buffer).  Rows received by a rank are grouped by
+ * (source rank, local expert).  None of these kernels waits on another GPU; the caller orders the
+ * ranks between the calls (a stream-ordered collective).
+ *
+ * mq_ep_plan: all_counts int32 [G,E] (per-expert slot counts of every rank) ->
+ *   send_base int32 [E]: row in the owner's receive buffer where this rank's rows of expert e start;
+ *   seg_offsets int32 [E+1]: prefix sums of this rank's G*(E/G) receive groups.
+ * mq_ep_dispatch: fused permute + dispatch.  Row p of the expert-sorted order (token perm[p]/K of x)
+ *   is written into the owner's receive buffer; slot_dst[p] = owner * cap_rows + row (or -1 and
+ *   status bit 2 when the row would not fit in cap_rows).
+ * mq_ep_combine: fused combine + unpermute.  out[t,:] = cast(sum_k weights[t,k] *
+ *   float(y_owner[slot_dst[inv[t*K+k]]])), fp32 multiply then add, k ascending.
+ */
+int mq_ep_plan(const int32_t* all_counts, int64_t G, int64_t rank, int64_t E,
+               int32_t* send_base, int32_t* seg_offsets, void* stream);
+int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, const int32_t* offsets,
+                   const int32_t* send_base, int64_t S, int64_t K, int64_t H, int64_t E, int64_t G,
+                   const uint64_t* peer_recv_ptrs, int64_t cap_rows, int32_t* slot_dst,
+                   int32_t* d_status, void* stream);
+int mq_ep_combine(const uint64_t* peer_y_ptrs, int dtype, const float* weights, const int32_t* inv,
+                  const int32_t* slot_dst, int64_t T, int64_t K, int64_t H, int64_t cap_rows,
+                  void* out, void* stream);
 
 #ifdef __cplusplus
 }

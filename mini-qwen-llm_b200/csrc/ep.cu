@@ -1,0 +1,178 @@
+// Expert-parallel exchange fused into the permute and combine kernels, over peer memory.
+//
+// The reference has no distributed code; the exchange exists because the 128 experts are sharded
+// over the GPUs of one NVSwitch box.  Instead of materialising the expert-sorted rows locally and
+// then moving them with a collective, the dispatch kernel gathers each token row straight into the
+// receive buffer of the GPU that owns its expert (16-byte peer stores over NVLink), and the combine
+// kernel reads each expert output row straight from the GPU that produced it (16-byte peer loads)
+// while forming the weighted sum.  No kernel here waits on another GPU: ordering between the ranks
+// is a stream-ordered collective issued by the host side between the kernels.
+//
+// Receive layout on every rank: rows grouped by (source rank, local expert), i.e. G * E_local groups,
+// which is the group order the grouped GEMM kernels take as it is.
+#include "common.cuh"
+
+namespace mq {
+namespace {
+
+// From the gathered per-expert counts [G, E]:
+//   send_base[e]  = row in the owner's receive buffer where this rank's rows for expert e start
+//   seg_offsets[] = prefix sums of this rank's own receive groups, (source, local expert) order
+__global__ void __launch_bounds__(256)
+ep_plan_kernel(const int32_t* __restrict__ all_counts, int G, int rank, int E,
+               int32_t* __restrict__ send_base, int32_t* __restrict__ seg_offsets) {
+  const int el = E / G;
+  // destination-side bases: one thread per expert, serial prefix over the (source, local expert) groups
+  // that precede (rank, e % el) on the owner of e.  G * el <= 1024 groups: a few hundred adds.
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int d = e / el, j = e - d * el;
+    int base = 0;
+    for (int s = 0; s < rank; ++s)
+      for (int jj = 0; jj < el; ++jj) base += all_counts[s * E + d * el + jj];
+    for (int jj = 0; jj < j; ++jj) base += all_counts[rank * E + d * el + jj];
+    send_base[e] = base;
+  }
+  // own receive groups
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int s = 0; s < G; ++s)
+      for (int j = 0; j < el; ++j) {
+        seg_offsets[s * el + j] = run;
+        run += all_counts[s * E + rank * el + j];
+      }
+    seg_offsets[G * el] = run;
+  }
+}
+
+// One warp per expert-sorted slot p: copy the token row to the owner's receive buffer.
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm,
+                   const int32_t* __restrict__ offsets, const int32_t* __restrict__ send_base,
+                   int64_t S, int K, int vec_per_row, int E, int el, const uint64_t* __restrict__ peer_recv,
+                   int64_t cap_rows, int32_t* __restrict__ slot_dst, int32_t* __restrict__ status) {
+  const int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (p >= S) return;
+  const int lane = threadIdx.x & 31;
+  // expert of sorted position p: last e with offsets[e] <= p
+  int lo = 0, hi = E;                       // invariant: offsets[lo] <= p < offsets[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (offsets[mid] <= (int)p) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const int d = e / el;
+  const int64_t row = (int64_t)send_base[e] + (p - offsets[e]);
+  if (row >= cap_rows) {                    // receive buffer too small for this routing: flag, do not write
+    if (lane == 0) { atomicOr(status, 2); slot_dst[p] = -1; }
+    return;
+  }
+  if (lane == 0) slot_dst[p] = (int32_t)(d * cap_rows + row);
+  const uint4* src = x + (int64_t)(perm[p] / K) * vec_per_row;
+  uint4* dst = reinterpret_cast<uint4*>(peer_recv[d]) + row * vec_per_row;
+  for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
+}
+
+// out[t,:] = cast(sum_k w[t,k] * float(y_on_owner[slot row, :])), fp32 multiply then add, k ascending.
+template <typename T>
+__global__ void __launch_bounds__(128)
+ep_combine_kernel(const uint64_t* __restrict__ peer_y, const float* __restrict__ weights,
+                  const int32_t* __restrict__ inv, const int32_t* __restrict__ slot_dst, int K, int64_t H,
+                  int64_t cap_rows, T* __restrict__ out) {
+  __shared__ const T* s_row[32];
+  __shared__ float s_w[32];
+  const int64_t t = blockIdx.x;
+  if (threadIdx.x < K) {
+    const int v = slot_dst[inv[t * K + threadIdx.x]];
+    const T* row = nullptr;
+    if (v >= 0) {
+      const int d = (int)(v / cap_rows);
+      row = reinterpret_cast<const T*>(peer_y[d]) + (int64_t)(v - d * cap_rows) * H;
+    }
+    s_row[threadIdx.x] = row;
+    s_w[threadIdx.x] = weights[t * K + threadIdx.x];
+  }
+  __syncthreads();
+  constexpr int V = 16 / sizeof(T);
+  const int64_t h0 = ((int64_t)blockIdx.y * 128 + threadIdx.x) * V;
+  if (h0 >= H) return;
+  float acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+  // peer loads go out eight at a time before their first use (NVLink latency is microseconds)
+  for (int k0 = 0; k0 < K; k0 += 8) {
+    uint4 raw[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const T* row = k0 + i < K ? s_row[k0 + i] : nullptr;
+      raw[i] = row ? *reinterpret_cast<const uint4*>(row + h0) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (k0 + i < K) {
+        const float wk = s_w[k0 + i];
+        const T* v = reinterpret_cast<const T*>(&raw[i]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(wk, to_float<T>(v[j])));
+      }
+    }
+  }
+  T o[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) o[j] = from_float<T>(acc[j]);
+  *reinterpret_cast<uint4*>(out + t * H + h0) = *reinterpret_cast<const uint4*>(o);
+}
+
+template <typename T>
+int launch_ep_combine(const uint64_t* peer_y, const float* weights, const int32_t* inv, const int32_t* slot_dst,
+                      int64_t T_, int K, int64_t H, int64_t cap_rows, void* out, cudaStream_t st) {
+  constexpr int V = 16 / sizeof(T);
+  dim3 grid((unsigned)T_, (unsigned)((H + 128 * V - 1) / (128 * V)));
+  ep_combine_kernel<T><<<grid, 128, 0, st>>>(peer_y, weights, inv, slot_dst, K, H, cap_rows, reinterpret_cast<T*>(out));
+  return check_launch();
+}
+
+}  // namespace
+}  // namespace mq
+
+extern "C" int mq_ep_plan(const int32_t* all_counts, int64_t G, int64_t rank, int64_t E,
+                          int32_t* send_base, int32_t* seg_offsets, void* stream) {
+  using namespace mq;
+  if (G <= 0 || E <= 0 || rank < 0 || rank >= G || E % G != 0) return MQ_ERR_INVALID_ARGUMENT;
+  if (E > 1024) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (!all_counts || !send_base || !seg_offsets) return MQ_ERR_INVALID_ARGUMENT;
+  ep_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(all_counts, (int)G, (int)rank, (int)E,
+                                                                       send_base, seg_offsets);
+  return check_launch();
+}
+
+extern "C" int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, const int32_t* offsets,
+                              const int32_t* send_base, int64_t S, int64_t K, int64_t H, int64_t E, int64_t G,
+                              const uint64_t* peer_recv_ptrs, int64_t cap_rows, int32_t* slot_dst,
+                              int32_t* d_status, void* stream) {
+  using namespace mq;
+  if (S < 0 || K <= 0 || H <= 0 || E <= 0 || G <= 0 || E % G != 0 || !valid_dtype(dtype)) return MQ_ERR_INVALID_ARGUMENT;
+  if (cap_rows <= 0 || G * cap_rows >= ((int64_t)1 << 31)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  const int64_t row_bytes = H * (int64_t)dtype_size(dtype);
+  if (row_bytes % 16 != 0) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (S == 0) return MQ_OK;
+  if (!x || !perm || !offsets || !send_base || !peer_recv_ptrs || !slot_dst || !d_status) return MQ_ERR_INVALID_ARGUMENT;
+  if (!aligned16(x)) return MQ_ERR_INVALID_ARGUMENT;
+  ep_dispatch_kernel<<<(unsigned)((S + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(x), perm, offsets, send_base, S, (int)K, (int)(row_bytes / 16), (int)E,
+      (int)(E / G), peer_recv_ptrs, cap_rows, slot_dst, d_status);
+  return check_launch();
+}
+
+extern "C" int mq_ep_combine(const uint64_t* peer_y_ptrs, int dtype, const float* weights, const int32_t* inv,
+                             const int32_t* slot_dst, int64_t T, int64_t K, int64_t H, int64_t cap_rows,
+                             void* out, void* stream) {
+  using namespace mq;
+  if (T < 0 || K <= 0 || H <= 0 || cap_rows <= 0 || !valid_dtype(dtype)) return MQ_ERR_INVALID_ARGUMENT;
+  if (K > 32 || (H * (int64_t)dtype_size(dtype)) % 16 != 0) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (T == 0) return MQ_OK;
+  if (!peer_y_ptrs || !weights || !inv || !slot_dst || !out || !aligned16(out)) return MQ_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == MQ_F32) return launch_ep_combine<float>(peer_y_ptrs, weights, inv, slot_dst, T, (int)K, H, cap_rows, out, st);
+  if (dtype == MQ_BF16) return launch_ep_combine<__nv_bfloat16>(peer_y_ptrs, weights, inv, slot_dst, T, (int)K, H, cap_rows, out, st);
+  return launch_ep_combine<__half>(peer_y_ptrs, weights, inv, slot_dst, T, (int)K, H, cap_rows, out, st);
+}

@@ -20,6 +20,7 @@ def moe_grouped_gemm(
     expert_offsets: torch.Tensor,    # [num_experts + 1]
     status: torch.Tensor | None = None,
     zero_init: bool = True,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """``out[s:t] = permuted_hidden[s:t] @ expert_weights[e].T`` per expert, fp32 accumulation.
 
@@ -38,7 +39,9 @@ def moe_grouped_gemm(
     a = permuted_hidden.contiguous()
     w = expert_weights.contiguous()
     S = a.shape[0]
-    out = (torch.zeros if zero_init else torch.empty)(S, D, dtype=a.dtype, device=a.device)
+    if out is None:
+        out = (torch.zeros if zero_init else torch.empty)(S, D, dtype=a.dtype, device=a.device)
+    assert out.is_contiguous() and tuple(out.shape) == (S, D) and out.dtype == a.dtype
     if status is None:
         status = _status_word(a.device)
     rc = _cabi.load().mq_grouped_gemm(_cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(_offsets32(expert_offsets)), S, groups, E, D, H,

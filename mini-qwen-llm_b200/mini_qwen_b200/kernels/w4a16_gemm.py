@@ -35,7 +35,7 @@ def _check_w4(x, qweight, scales, qzeros, group_size, E):
 
 
 def w4a16_grouped_gemm(x, qweight, scales, qzeros, expert_offsets, group_size: int = 128,
-                       zero_init: bool = True) -> torch.Tensor:
+                       zero_init: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
     """Rows ``offsets[e]:offsets[e+1]`` of x times the dequantised weight of expert e.
     qweight [E, K/8, N], scales [E, K/g, N], qzeros [E, K/g, N/8], offsets int32 [E+1]."""
     E = qweight.shape[0]
@@ -44,7 +44,9 @@ def w4a16_grouped_gemm(x, qweight, scales, qzeros, expert_offsets, group_size: i
     assert groups >= E and groups % E == 0
     x = x.contiguous()
     S = x.shape[0]
-    out = (torch.zeros if zero_init else torch.empty)(S, N, dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        out = (torch.zeros if zero_init else torch.empty)(S, N, dtype=torch.bfloat16, device=x.device)
+    assert out.is_contiguous() and tuple(out.shape) == (S, N) and out.dtype == torch.bfloat16
     rc = _cabi.load().mq_w4a16_grouped_gemm(_cabi.ptr(x), _cabi.ptr(qweight), _cabi.ptr(scales), _cabi.ptr(qzeros),
                                             _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size, _cabi.ptr(out),
                                             _cabi.stream_ptr(x.device))

@@ -55,7 +55,7 @@ class Qwen3MoEBlock(nn.Module):
     the other ranks in one all-to-all each way (see ``mini_qwen_b200.parallel``).
     """
 
-    def __init__(self, config, ep_group=None):
+    def __init__(self, config, ep_group=None, ep_mode: str = "p2p", ep_max_tokens: int | None = None):
         super().__init__()
         self.num_experts = config.num_experts
         self.num_experts_per_tok = config.num_experts_per_tok
@@ -64,6 +64,11 @@ class Qwen3MoEBlock(nn.Module):
         self._stacked_epoch = -1
         self._stacks = None
         self.ep_group = ep_group
+        # "p2p": dispatch/combine fused into the permute/unpermute kernels over peer memory (CUDA only);
+        # "nccl": materialise, then torch.distributed all-to-all (any backend; one host sync per call)
+        self.ep_mode = ep_mode
+        self.ep_max_tokens = ep_max_tokens     # most tokens per rank and call (sizes the peer buffers)
+        self._peer = None
         self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
         self.ep_rank = 0 if ep_group is None else torch.distributed.get_rank(ep_group)
         if self.num_experts % self.ep_size != 0:
@@ -127,7 +132,8 @@ class Qwen3MoEBlock(nn.Module):
 
     @classmethod
     def from_stacked(cls, config, router_weight: torch.Tensor, gate_up_proj: torch.Tensor,
-                     down_proj: torch.Tensor, ep_group=None) -> "Qwen3MoEBlock":
+                     down_proj: torch.Tensor, ep_group=None, ep_mode: str = "p2p",
+                     ep_max_tokens: int | None = None) -> "Qwen3MoEBlock":
         """Builds a dense block from expert-major tensors without copying them:
         ``router_weight`` [E, H], ``gate_up_proj`` [E, 2I, H] (gate rows, then up rows: the fused
         layout of HF Qwen3-MoE checkpoints), ``down_proj`` [E, H, I].  The per-expert modules become
@@ -135,7 +141,7 @@ class Qwen3MoEBlock(nn.Module):
         only (``num_experts / G`` of them); the router weight always covers all experts."""
         E, I2, H = gate_up_proj.shape
         with torch.device("meta"):
-            blk = cls(config, ep_group=ep_group)
+            blk = cls(config, ep_group=ep_group, ep_mode=ep_mode, ep_max_tokens=ep_max_tokens)
         assert E == blk.num_local_experts and I2 == 2 * config.intermediate_size and H == config.hidden_size
         assert tuple(down_proj.shape) == (E, H, I2 // 2)
         assert tuple(router_weight.shape) == (config.num_experts, H)
@@ -171,6 +177,8 @@ class Qwen3MoEBlock(nn.Module):
         _, weights, ids32 = run("router", moe_router, x2d, self.gate.weight, K, bias=self.router_bias,
                                 renormalize=self.norm_topk_prob, return_int32_ids=True)
         perm, inv, off32, _ = run("permute_plan", moe_permute_plan, ids32, E, want_int64_offsets=False)
+        if self.ep_size > 1 and self.ep_mode == "p2p":
+            return self._forward_peer(x2d, st, weights, perm, inv, off32, T, K, E).reshape(shape)
         plan = None
         if self.ep_size > 1:
             all_counts = parallel.gather_counts(off32[1:] - off32[:-1], self.ep_group)
@@ -179,19 +187,44 @@ class Qwen3MoEBlock(nn.Module):
             plan = parallel.make_plan(all_counts, self.ep_rank)
             permuted = run("dispatch", parallel.dispatch, permuted, plan, self.ep_group)
             off32 = plan.seg_offsets
-        if st["w4"]:
-            # the offsets of a routing cover every slot, so no output needs a zero fill
-            h = run("grouped_swiglu", w4a16_grouped_swiglu, permuted, st["gate_proj"], st["up_proj"], off32,
-                    st["group_size"], zero_init=False)
-            out_perm = run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off32, st["group_size"],
-                           zero_init=False)
-        else:
-            h = run("grouped_swiglu", moe_grouped_swiglu, permuted, st["w13"], off32, zero_init=False)
-            out_perm = run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False)
+        out_perm = self._experts(st, permuted, off32)
         if plan is not None:
             out_perm = run("combine", parallel.combine, out_perm, plan, self.ep_group)
         out = run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K)
         return out.reshape(shape)
+
+    def _experts(self, st, rows, off32, out=None):
+        """Grouped gate/up + SwiGLU and down projection over rows grouped by `off32`."""
+        run = self._stage
+        # the groups of a routing cover every row that is read later, so no output needs a zero fill
+        if st["w4"]:
+            h = run("grouped_swiglu", w4a16_grouped_swiglu, rows, st["gate_proj"], st["up_proj"], off32,
+                    st["group_size"], zero_init=False)
+            return run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off32, st["group_size"],
+                       zero_init=False, out=out)
+        h = run("grouped_swiglu", moe_grouped_swiglu, rows, st["w13"], off32, zero_init=False)
+        return run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False, out=out)
+
+    def _forward_peer(self, x2d, st, weights, perm, inv, off32, T, K, E):
+        """Expert-parallel path over peer memory: rows go straight from x into the owners' receive
+        buffers and expert outputs are read straight from the owners while combining."""
+        run = self._stage
+        if self._peer is None:
+            max_t = self.ep_max_tokens or T
+            self._peer = parallel.PeerExchange(self.ep_group, x2d.device, self.ep_size * max_t * K, x2d.shape[1],
+                                               x2d.dtype)
+            self.ep_max_tokens = max_t
+        peer = self._peer
+        if T > self.ep_max_tokens or x2d.dtype != peer.dtype:
+            raise ValueError(f"expert-parallel buffers were sized for {self.ep_max_tokens} tokens of {peer.dtype} per "
+                             f"rank; got {T} of {x2d.dtype} (pass ep_max_tokens at construction)")
+        all_counts = run("counts_allgather", parallel.gather_counts, off32[1:] - off32[:-1], self.ep_group)
+        send_base, seg = run("ep_plan", peer.plan, all_counts)
+        slot_dst = run("dispatch", peer.dispatch, x2d, perm, off32, send_base, K, E)
+        run("rank_barrier", peer.rank_barrier)
+        self._experts(st, peer.recv_rows(), seg, out=peer.y_rows())
+        run("rank_barrier", peer.rank_barrier)
+        return run("combine", peer.combine, weights, inv, slot_dst, T, K)
 
     def _stage(self, name, fn, *args, **kwargs):
         """Runs one stage; with ``kernel_events`` set, brackets it with CUDA events on the current stream."""

@@ -83,3 +83,90 @@ def combine(rows: torch.Tensor, plan: ExchangePlan, group=None) -> torch.Tensor:
     dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=plan.send_splits,
                            input_split_sizes=plan.recv_splits, group=group)
     return out
+
+
+class PeerExchange:
+    """Buffers and kernels for the exchange over peer memory (NVLink loads/stores), one per block.
+
+    Every rank owns a receive buffer and an expert-output buffer of ``cap_rows`` rows that all ranks
+    of the group can address (torch symmetric memory supplies the allocation and the peer
+    addresses; the data path is this library's kernels).  ``cap_rows`` defaults to the worst case,
+    every slot of every rank landing on one GPU, so no routing can overflow it.
+
+    Ordering between ranks is two stream-ordered collectives per layer call (a one-element
+    all-reduce): after the dispatch kernels and after the down projection.  No kernel spins on
+    another GPU.
+    """
+
+    def __init__(self, group, device, cap_rows: int, hidden: int, dtype: torch.dtype):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _cabi
+        self._cabi = _cabi
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.cap_rows, self.hidden, self.dtype = cap_rows, hidden, dtype
+        if self.world * cap_rows >= 2 ** 31:
+            raise ValueError("expert-parallel buffer too large for 32-bit slot addresses")
+        self.recv = symm_mem.empty(cap_rows * hidden, dtype=dtype, device=device)
+        self.y = symm_mem.empty(cap_rows * hidden, dtype=dtype, device=device)
+        h_recv = symm_mem.rendezvous(self.recv, group)
+        h_y = symm_mem.rendezvous(self.y, group)
+        self._handles = (h_recv, h_y)
+        self.recv_ptrs = torch.tensor(list(h_recv.buffer_ptrs), dtype=torch.int64, device=device)
+        self.y_ptrs = torch.tensor(list(h_y.buffer_ptrs), dtype=torch.int64, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def recv_rows(self) -> torch.Tensor:
+        return self.recv.view(self.cap_rows, self.hidden)
+
+    def y_rows(self) -> torch.Tensor:
+        return self.y.view(self.cap_rows, self.hidden)
+
+    def rank_barrier(self) -> None:
+        """Stream-ordered barrier across the group: returns (on the stream) once every rank's earlier
+        kernels have finished."""
+        dist.all_reduce(self._token, group=self.group)
+
+    def plan(self, all_counts: torch.Tensor):
+        """Device-side plan (no host sync): (send_base int32 [E], seg_offsets int32 [E+1])."""
+        G, E = all_counts.shape
+        dev = all_counts.device
+        send_base = torch.empty(E, dtype=torch.int32, device=dev)
+        seg = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        c = self._cabi
+        rc = c.load().mq_ep_plan(c.ptr(all_counts), G, self.rank, E, c.ptr(send_base), c.ptr(seg), c.stream_ptr(dev))
+        c.check(rc, "mq_ep_plan")
+        c.count_launches(1)
+        return send_base, seg
+
+    def dispatch(self, x: torch.Tensor, perm, off32, send_base, top_k: int, num_experts: int) -> torch.Tensor:
+        """Fused permute + dispatch; returns slot_dst int32 [S] (owner * cap_rows + row)."""
+        c = self._cabi
+        S = perm.numel()
+        slot_dst = torch.empty(S, dtype=torch.int32, device=x.device)
+        rc = c.load().mq_ep_dispatch(c.ptr(x), c.dtype_code(x), c.ptr(perm), c.ptr(off32), c.ptr(send_base), S, top_k,
+                                     x.shape[1], num_experts, self.world, c.ptr(self.recv_ptrs), self.cap_rows,
+                                     c.ptr(slot_dst), c.ptr(self.status), c.stream_ptr(x.device))
+        c.check(rc, "mq_ep_dispatch")
+        c.count_launches(1 if S else 0)
+        return slot_dst
+
+    def combine(self, weights, inv, slot_dst, num_tokens: int, top_k: int) -> torch.Tensor:
+        """Fused combine + unpermute from the owners' output buffers."""
+        c = self._cabi
+        out = torch.empty(num_tokens, self.hidden, dtype=self.dtype, device=weights.device)
+        rc = c.load().mq_ep_combine(c.ptr(self.y_ptrs), c.dtype_code(out), c.ptr(weights), c.ptr(inv), c.ptr(slot_dst),
+                                    num_tokens, top_k, self.hidden, self.cap_rows, c.ptr(out),
+                                    c.stream_ptr(weights.device))
+        c.check(rc, "mq_ep_combine")
+        c.count_launches(1 if num_tokens else 0)
+        return out
+
+    def check_status(self) -> None:
+        """Raises if a receive buffer overflowed (synchronises)."""
+        if int(self.status.item()) & 2:
+            raise RuntimeError("expert-parallel receive buffer overflowed; construct the block with a larger "
+                               "ep_max_tokens / capacity")

@@ -17,7 +17,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, w4):
+def _worker(rank, world, port, w4, mode):
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     for p in (root, os.path.join(root, "mini-qwen-llm_b200")):
@@ -43,12 +43,12 @@ def _worker(rank, world, port, w4):
             lay = synthetic.dense_layer(21, T_local * world, H, E, K, I, torch.bfloat16)
             w13 = torch.cat([lay.gate[lo:hi], lay.up[lo:hi]], dim=1).to(dev)
             blk = Qwen3MoEBlock.from_stacked(cfg, lay.router.to(dev), w13, lay.down[lo:hi].to(dev),
-                                             ep_group=dist.group.WORLD)
+                                             ep_group=dist.group.WORLD, ep_mode=mode)
             ref, ref_ids, _, _ = O.block_forward(lay.x, lay.router, lay.gate, lay.up, lay.down, K, True, bias)
             router_w = lay.router
         else:
             lay = synthetic.w4a16_layer(22, T_local * world, H, E, K, I, group=128)
-            blk = Qwen3MoEBlock(cfg, ep_group=dist.group.WORLD)
+            blk = Qwen3MoEBlock(cfg, ep_group=dist.group.WORLD, ep_mode=mode)
             for j, ex in enumerate(blk.experts):
                 e = lo + j
                 for name, p in (("gate_proj", lay.gate), ("up_proj", lay.up), ("down_proj", lay.down)):
@@ -72,14 +72,19 @@ def _worker(rank, world, port, w4):
         ok = err <= 2e-3 * max(1.0, want.abs().max().item()) + 2e-2 * want.abs()
         assert bool(ok.all()), f"rank {rank}: max err {err.max().item()}"
         assert torch.equal(blk(x), out)                      # deterministic across calls
+        if mode == "p2p":
+            blk._peer.check_status()                          # no receive-buffer overflow
+            out_small = blk(x[:17])                          # fewer tokens than the buffers were sized for
+            assert out_small.shape == (17, H)
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("mode", ["p2p", "nccl"])
 @pytest.mark.parametrize("w4", [False, True])
-def test_expert_parallel_block_matches_oracle(w4):
+def test_expert_parallel_block_matches_oracle(w4, mode):
     world = torch.cuda.device_count()
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
     world = 2 if world < 4 else 4
-    mp.spawn(_worker, args=(world, _free_port(), w4), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), w4, mode), nprocs=world, join=True)
