@@ -187,6 +187,15 @@ int mq_w4a16_grouped_swiglu(const void* x,
  * mq_ep_combine: fused combine + unpermute.  out[t,:] = cast(sum_k weights[t,k] *
  *   float(y_owner[slot_dst[inv[t*K+k]]])), fp32 multiply then add, k ascending.
  */
+/* mq_ep_share_counts: writes this rank's per-expert counts (from its offsets [E+1]) into row `rank`
+ *   of every peer's counts table int32 [G,E] (peer_counts_ptrs: G base addresses).
+ * mq_ep_barrier: stream-ordered barrier across the G ranks through a signal array int32 [G] on every
+ *   rank (peer_signal_ptrs) and a local epoch counter.  The wait is bounded (about a second); on
+ *   expiry MQ_DEV_WAIT_EXPIRED is set in d_status and the kernel returns. */
+int mq_ep_share_counts(const int32_t* offsets, int64_t E, int64_t G, int64_t rank,
+                       const uint64_t* peer_counts_ptrs, void* stream);
+int mq_ep_barrier(const uint64_t* peer_signal_ptrs, int32_t* epoch_counter, int64_t G, int64_t rank,
+                  int32_t* d_status, void* stream);
 int mq_ep_plan(const int32_t* all_counts, int64_t G, int64_t rank, int64_t E,
                int32_t* send_base, int32_t* seg_offsets, void* stream);
 int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, const int32_t* offsets,

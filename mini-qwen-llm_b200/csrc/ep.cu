@@ -44,6 +44,49 @@ ep_plan_kernel(const int32_t* __restrict__ all_counts, int G, int rank, int E,
   }
 }
 
+// Per-expert slot counts of this rank (differences of its offsets) into row `rank` of every peer's
+// counts table: an all-gather made of E * G 4-byte peer stores.
+__global__ void __launch_bounds__(256)
+ep_share_counts_kernel(const int32_t* __restrict__ offsets, int E, int G, int rank,
+                       const uint64_t* __restrict__ peer_counts) {
+  for (int i = threadIdx.x; i < E * G; i += blockDim.x) {
+    const int d = i / E, e = i - d * E;
+    reinterpret_cast<int32_t*>(peer_counts[d])[rank * E + e] = offsets[e + 1] - offsets[e];
+  }
+}
+
+// Barrier across the ranks of the group, on the stream: every rank bumps its epoch, writes it into its
+// slot of every peer's signal array and waits until all slots of its own array have reached the epoch.
+// The wait is bounded; when it runs out the kernel records MQ_DEV_WAIT_EXPIRED and returns, so a
+// missing rank costs a second, not a hang.
+constexpr uint32_t EP_SPIN_LIMIT = 1u << 22;
+
+__global__ void __launch_bounds__(32)
+ep_barrier_kernel(const uint64_t* __restrict__ peer_sig, int32_t* __restrict__ epoch_ctr, int G, int rank,
+                  int32_t* __restrict__ status) {
+  __shared__ int s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = *epoch_ctr + 1;
+    *epoch_ctr = s_epoch;
+  }
+  __syncwarp();
+  const int epoch = s_epoch;
+  __threadfence_system();                        // earlier kernels' peer stores are complete; order the flag behind them
+  for (int r = threadIdx.x; r < G; r += 32) {
+    int32_t* remote = reinterpret_cast<int32_t*>(peer_sig[r]) + rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  }
+  const int32_t* mine = reinterpret_cast<const int32_t*>(peer_sig[rank]);
+  for (int r = threadIdx.x; r < G; r += 32) {
+    uint32_t spin = 0;
+    int v;
+    do {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine + r) : "memory");
+    } while (v < epoch && ++spin < EP_SPIN_LIMIT);
+    if (v < epoch) atomicOr(status, (int)MQ_DEV_WAIT_EXPIRED);
+  }
+}
+
 // One warp per expert-sorted slot p: copy the token row to the owner's receive buffer.
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm,
@@ -142,6 +185,24 @@ extern "C" int mq_ep_plan(const int32_t* all_counts, int64_t G, int64_t rank, in
   if (!all_counts || !send_base || !seg_offsets) return MQ_ERR_INVALID_ARGUMENT;
   ep_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(all_counts, (int)G, (int)rank, (int)E,
                                                                        send_base, seg_offsets);
+  return check_launch();
+}
+
+extern "C" int mq_ep_share_counts(const int32_t* offsets, int64_t E, int64_t G, int64_t rank,
+                                  const uint64_t* peer_counts_ptrs, void* stream) {
+  using namespace mq;
+  if (E <= 0 || G <= 0 || rank < 0 || rank >= G || !offsets || !peer_counts_ptrs) return MQ_ERR_INVALID_ARGUMENT;
+  ep_share_counts_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(offsets, (int)E, (int)G, (int)rank,
+                                                                                peer_counts_ptrs);
+  return check_launch();
+}
+
+extern "C" int mq_ep_barrier(const uint64_t* peer_signal_ptrs, int32_t* epoch_counter, int64_t G, int64_t rank,
+                             int32_t* d_status, void* stream) {
+  using namespace mq;
+  if (G <= 0 || rank < 0 || rank >= G || !peer_signal_ptrs || !epoch_counter || !d_status) return MQ_ERR_INVALID_ARGUMENT;
+  ep_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(peer_signal_ptrs, epoch_counter, (int)G,
+                                                                          (int)rank, d_status);
   return check_launch();
 }
 

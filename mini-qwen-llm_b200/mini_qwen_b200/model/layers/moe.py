@@ -218,7 +218,8 @@ class Qwen3MoEBlock(nn.Module):
         if T > self.ep_max_tokens or x2d.dtype != peer.dtype:
             raise ValueError(f"expert-parallel buffers were sized for {self.ep_max_tokens} tokens of {peer.dtype} per "
                              f"rank; got {T} of {x2d.dtype} (pass ep_max_tokens at construction)")
-        all_counts = run("counts_allgather", parallel.gather_counts, off32[1:] - off32[:-1], self.ep_group)
+        all_counts = run("share_counts", peer.share_counts, off32)
+        run("rank_barrier", peer.rank_barrier)
         send_base, seg = run("ep_plan", peer.plan, all_counts)
         slot_dst = run("dispatch", peer.dispatch, x2d, perm, off32, send_base, K, E)
         run("rank_barrier", peer.rank_barrier)

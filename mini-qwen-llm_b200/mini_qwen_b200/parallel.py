@@ -93,9 +93,10 @@ class PeerExchange:
     addresses; the data path is this library's kernels).  ``cap_rows`` defaults to the worst case,
     every slot of every rank landing on one GPU, so no routing can overflow it.
 
-    Ordering between ranks is two stream-ordered collectives per layer call (a one-element
-    all-reduce): after the dispatch kernels and after the down projection.  No kernel spins on
-    another GPU.
+    Ordering between ranks is three stream-ordered barriers per layer call: after the counts have
+    been shared, after the dispatch kernels and after the down projection.  The barrier is a
+    one-warp kernel that writes an epoch into every peer's signal array and polls its own, with a
+    bounded number of polls (an expired wait sets a status bit; it never hangs).
     """
 
     def __init__(self, group, device, cap_rows: int, hidden: int, dtype: torch.dtype):
@@ -117,7 +118,16 @@ class PeerExchange:
         self.recv_ptrs = torch.tensor(list(h_recv.buffer_ptrs), dtype=torch.int64, device=device)
         self.y_ptrs = torch.tensor(list(h_y.buffer_ptrs), dtype=torch.int64, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+        self._counts = None            # symmetric [G, E] int32, created on first use (E is not known here)
+        self._sig = symm_mem.empty(max(self.world, 32), dtype=torch.int32, device=device)
+        self._sig.zero_()
+        h_sig = symm_mem.rendezvous(self._sig, group)
+        self.sig_ptrs = torch.tensor(list(h_sig.buffer_ptrs), dtype=torch.int64, device=device)
+        self._epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self._symm = symm_mem
+        self._handles += (h_sig,)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)      # every rank's signal array is zeroed before anyone signals
 
     def recv_rows(self) -> torch.Tensor:
         return self.recv.view(self.cap_rows, self.hidden)
@@ -126,9 +136,31 @@ class PeerExchange:
         return self.y.view(self.cap_rows, self.hidden)
 
     def rank_barrier(self) -> None:
-        """Stream-ordered barrier across the group: returns (on the stream) once every rank's earlier
-        kernels have finished."""
-        dist.all_reduce(self._token, group=self.group)
+        """Stream-ordered barrier across the group: kernels launched after it start once every rank's
+        kernels launched before it have finished."""
+        c = self._cabi
+        dev = self.status.device
+        rc = c.load().mq_ep_barrier(c.ptr(self.sig_ptrs), c.ptr(self._epoch), self.world, self.rank,
+                                    c.ptr(self.status), c.stream_ptr(dev))
+        c.check(rc, "mq_ep_barrier")
+        c.count_launches(1)
+
+    def share_counts(self, off32: torch.Tensor) -> torch.Tensor:
+        """All-gather of the per-expert counts by peer stores; returns this rank's [G, E] table, valid
+        after the next rank_barrier()."""
+        E = off32.numel() - 1
+        dev = off32.device
+        if self._counts is None or self._counts.numel() != self.world * E:
+            self._counts = self._symm.empty(self.world * E, dtype=torch.int32, device=dev)
+            h = self._symm.rendezvous(self._counts, self.group)
+            self._handles += (h,)
+            self.counts_ptrs = torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=dev)
+        c = self._cabi
+        rc = c.load().mq_ep_share_counts(c.ptr(off32), E, self.world, self.rank, c.ptr(self.counts_ptrs),
+                                         c.stream_ptr(dev))
+        c.check(rc, "mq_ep_share_counts")
+        c.count_launches(1)
+        return self._counts.view(self.world, E)
 
     def plan(self, all_counts: torch.Tensor):
         """Device-side plan (no host sync): (send_base int32 [E], seg_offsets int32 [E+1])."""
@@ -167,6 +199,9 @@ class PeerExchange:
 
     def check_status(self) -> None:
         """Raises if a receive buffer overflowed (synchronises)."""
-        if int(self.status.item()) & 2:
+        bits = int(self.status.item())
+        if bits & 2:
             raise RuntimeError("expert-parallel receive buffer overflowed; construct the block with a larger "
                                "ep_max_tokens / capacity")
+        if bits & 1:
+            raise RuntimeError("an expert-parallel barrier timed out: a rank of the group did not arrive")
