@@ -31,7 +31,8 @@ H, E, TOPK, I = 2048, 128, 8, 768
 T_PREFILL = 4096
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
-CPU_SAMPLE_T = 512
+CPU_SAMPLE_T = 2048
+WORKLOAD = f"bf16 prefill MoE layer, T={T_PREFILL} tokens per GPU, H={H} E={E} top{TOPK} I={I} (seed 1)"
 
 
 def measured_peaks():
@@ -220,8 +221,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"bf16 prefill MoE layer T={T_PREFILL} H={H} E={E} top{TOPK} I={I} (seed 1), "
-                               "reference per-expert loop on host cores"},
+        "config": {"workload": WORKLOAD, "sample": sample,
+                   "parallelism": "reference per-expert loop (CPU restatement) on the host cores of rank 0"},
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -362,7 +363,7 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"bf16 prefill MoE layer T={T} per GPU, H={H} E={E} top{TOPK} I={I} (seed 1)",
+        "config": {"workload": WORKLOAD,
                    "l2": "per-step working set 1.2 GB of expert weights > 126 MB L2; no flush needed",
                    "parallelism": "single GPU" if world == 1 else
                    f"expert parallel ep{world}: {E // world} experts per GPU, {T} tokens per GPU, "
@@ -377,7 +378,8 @@ def run_ours(args):
     if world == 1 and not args.no_decode:
         del blk
         torch.cuda.empty_cache()
-        line["w4a16_decode"] = w4a16_decode_numbers(dev, peaks)
+        batches = tuple(int(b) for b in args.decode_batches.split(","))
+        line["w4a16_decode"] = w4a16_decode_numbers(dev, peaks, iters=args.decode_iters, batches=batches)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -391,9 +393,20 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the W4A16 decode numbers")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="only the W4A16 decode numbers (small profiling runs); prints their JSON list")
+    ap.add_argument("--decode-iters", type=int, default=200)
+    ap.add_argument("--decode-batches", default="1,8,16,64")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.decode_only:
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        batches = tuple(int(b) for b in args.decode_batches.split(","))
+        print(json.dumps({"w4a16_decode": w4a16_decode_numbers(dev, measured_peaks(), iters=args.decode_iters,
+                                                                batches=batches)}))
     else:
         run_ours(args)
 

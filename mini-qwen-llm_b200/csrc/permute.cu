@@ -105,19 +105,29 @@ permute_hist(const void* __restrict__ ids, int64_t S, int E, int32_t* __restrict
 }
 
 // seg_hist[seg][e] -> exclusive prefix over segments (in place), offsets[e] = exclusive prefix of totals.
+// A warp takes an expert at a time and scans its segment counts 32 at a time (shuffle scan + carry),
+// so the loads of a chunk are independent instead of a serial read-modify-write chain.
 __global__ void __launch_bounds__(P_THREADS)
 permute_scan(int32_t* __restrict__ seg_hist, int nseg, int E,
              int64_t* __restrict__ off64, int32_t* __restrict__ off32) {
   __shared__ int tot[P_MAX_E];
   __shared__ int warp_tot[P_THREADS / 32];
-  for (int e = threadIdx.x; e < E; e += P_THREADS) {
-    int run = 0;
-    for (int s = 0; s < nseg; ++s) {
-      int c = seg_hist[(size_t)s * E + e];
-      seg_hist[(size_t)s * E + e] = run;
-      run += c;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = warp; e < E; e += P_THREADS / 32) {
+    int carry = 0;
+    for (int s0 = 0; s0 < nseg; s0 += 32) {
+      const int sidx = s0 + lane;
+      const int c = sidx < nseg ? seg_hist[(size_t)sidx * E + e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      if (sidx < nseg) seg_hist[(size_t)sidx * E + e] = carry + incl - c;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    tot[e] = run;
+    if (lane == 0) tot[e] = carry;
   }
   __syncthreads();
   int total = block_exclusive_scan(tot, E, warp_tot);

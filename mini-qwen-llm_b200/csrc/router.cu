@@ -200,13 +200,19 @@ router_logits_mma(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w
     for (int i = 0; i < 4; ++i) { master[n][i] = 0.0f; part[n][i] = 0.0f; }
 
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  // the loads of block k+32 are issued before the MMAs of block k
+  uint4 va = zero4, vb = zero4, vw[4] = {zero4, zero4, zero4, zero4};
+  auto fetch = [&](int64_t k, uint4& a, uint4& b, uint4 (&wv)[4]) {
+    a = ra_ok ? __ldg(reinterpret_cast<const uint4*>(xa + k)) : zero4;
+    b = rb_ok ? __ldg(reinterpret_cast<const uint4*>(xb + k)) : zero4;
+#pragma unroll
+    for (int n = 0; n < 4; ++n) wv[n] = w_ok[n] ? __ldg(reinterpret_cast<const uint4*>(wp[n] + k)) : zero4;
+  };
+  if (k_lo < k_hi) fetch(k_lo, va, vb, vw);
   int in_chunk = 0;
   for (int64_t k = k_lo; k < k_hi; k += 32) {
-    const uint4 va = ra_ok ? __ldg(reinterpret_cast<const uint4*>(xa + k)) : zero4;
-    const uint4 vb = rb_ok ? __ldg(reinterpret_cast<const uint4*>(xb + k)) : zero4;
-    uint4 vw[4];
-#pragma unroll
-    for (int n = 0; n < 4; ++n) vw[n] = w_ok[n] ? __ldg(reinterpret_cast<const uint4*>(wp[n] + k)) : zero4;
+    uint4 na = zero4, nb = zero4, nw[4] = {zero4, zero4, zero4, zero4};
+    if (k + 32 < k_hi) fetch(k + 32, na, nb, nw);
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
       mma16816(part[n], va.x, vb.x, va.y, vb.y, vw[n].x, vw[n].y, bf);
@@ -219,6 +225,9 @@ router_logits_mma(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w
 #pragma unroll
         for (int i = 0; i < 4; ++i) { master[n][i] += part[n][i]; part[n][i] = 0.0f; }
     }
+    va = na; vb = nb;
+#pragma unroll
+    for (int n = 0; n < 4; ++n) vw[n] = nw[n];
   }
 #pragma unroll
   for (int n = 0; n < 4; ++n)

@@ -78,6 +78,7 @@ class Qwen3MoEBlock(nn.Module):
         self.gate = nn.Linear(config.hidden_size, config.num_experts, bias=False)
         self.experts = nn.ModuleList([_ExpertMLP(config, self._epoch) for _ in range(self.num_local_experts)])
         self.router_bias = None       # optional fp32 [E] logit bias (not in the reference)
+        self._status = None
         self.kernel_events = None     # set to a list to collect (stage, start, end) CUDA events per forward
 
     # ------------------------------------------------------------------ weight stacks
@@ -202,8 +203,22 @@ class Qwen3MoEBlock(nn.Module):
                     st["group_size"], zero_init=False)
             return run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off32, st["group_size"],
                        zero_init=False, out=out)
-        h = run("grouped_swiglu", moe_grouped_swiglu, rows, st["w13"], off32, zero_init=False)
-        return run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False, out=out)
+        status = self._status_word(rows.device)
+        h = run("grouped_swiglu", moe_grouped_swiglu, rows, st["w13"], off32, zero_init=False, status=status)
+        return run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False, out=out, status=status)
+
+    def _status_word(self, device) -> torch.Tensor:
+        """Device status word of this block's kernels (bit 0: a bounded wait expired); allocated once."""
+        if self._status is None or self._status.device != device:
+            self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._status
+
+    def check_status(self) -> None:
+        """Raises if a kernel of this block reported a device-side error (synchronises)."""
+        if self._status is not None and int(self._status.item()) & 1:
+            raise RuntimeError("a bounded wait expired inside a grouped GEMM kernel; the last output is invalid")
+        if self._peer is not None:
+            self._peer.check_status()
 
     def _forward_peer(self, x2d, st, weights, perm, inv, off32, T, K, E):
         """Expert-parallel path over peer memory: rows go straight from x into the owners' receive
