@@ -350,7 +350,10 @@ def run_ours(args):
         achieved = gemm1_flops / (gemm1_ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": "grouped gate/up GEMM + SwiGLU", "achieved": achieved,
                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                    "peak_source": f"{peaks['source']} burst bf16 GEMM", "traffic": None,
+                    "peak_source": f"{peaks['source']} burst bf16 GEMM",
+                    # dram__bytes_read.sum + dram__bytes_write.sum of this kernel at this workload, one ncu
+                    # capture (profiles/grouped_gemm_tc5_c2.md); algorithmic bytes are 989e6
+                    "traffic": 1006.1e6 if world == 1 else None,
                     "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms}
 
     cpu_base = None
