@@ -354,7 +354,11 @@ def run_ours(args):
                     # dram__bytes_read.sum + dram__bytes_write.sum of this kernel at this workload, one ncu
                     # capture (profiles/grouped_gemm_tc5_c2.md); algorithmic bytes are 989e6
                     "traffic": 1006.1e6 if world == 1 else None,
-                    "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms}
+                    "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms,
+                    # the layer is on the ridge: the same launch seen from the HBM side (algorithmic bytes:
+                    # 805 MB weights + 134 MB rows + 50 MB h)
+                    "hbm": {"achieved": 989.0e6 / (gemm1_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": 989.0e6 / (gemm1_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
 
     cpu_base = None
     if world == 1 and not args.no_cpu_baseline:
