@@ -101,52 +101,57 @@ permute_hist(const void* __restrict__ ids, int64_t S, int E, int32_t* __restrict
     if ((unsigned)e < (unsigned)E) atomicAdd(&hist[e], 1);
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += P_THREADS) seg_hist[(size_t)blockIdx.x * E + e] = hist[e];
+  // stored expert-major [E][nseg] so that the scan over segments reads contiguous memory
+  for (int e = threadIdx.x; e < E; e += P_THREADS) seg_hist[(size_t)e * gridDim.x + blockIdx.x] = hist[e];
 }
 
-// seg_hist[seg][e] -> exclusive prefix over segments (in place), offsets[e] = exclusive prefix of totals.
-// A warp takes an expert at a time and scans its segment counts 32 at a time (shuffle scan + carry),
-// so the loads of a chunk are independent instead of a serial read-modify-write chain.
+// seg_hist[e][seg] -> exclusive prefix over segments (in place) and totals[e]; one warp per expert,
+// 32 segments at a time (coalesced loads, shuffle scan, carry).
 __global__ void __launch_bounds__(P_THREADS)
-permute_scan(int32_t* __restrict__ seg_hist, int nseg, int E,
-             int64_t* __restrict__ off64, int32_t* __restrict__ off32) {
-  __shared__ int tot[P_MAX_E];
-  __shared__ int warp_tot[P_THREADS / 32];
+permute_scan(int32_t* __restrict__ seg_hist, int nseg, int E, int32_t* __restrict__ totals) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int e = warp; e < E; e += P_THREADS / 32) {
-    int carry = 0;
-    for (int s0 = 0; s0 < nseg; s0 += 32) {
-      const int sidx = s0 + lane;
-      const int c = sidx < nseg ? seg_hist[(size_t)sidx * E + e] : 0;
-      int incl = c;
+  const int e = blockIdx.x * (P_THREADS / 32) + warp;
+  if (e >= E) return;
+  int32_t* row = seg_hist + (size_t)e * nseg;
+  int carry = 0;
+  for (int s0 = 0; s0 < nseg; s0 += 32) {
+    const int sidx = s0 + lane;
+    const int c = sidx < nseg ? row[sidx] : 0;
+    int incl = c;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += n;
-      }
-      if (sidx < nseg) seg_hist[(size_t)sidx * E + e] = carry + incl - c;
-      carry += __shfl_sync(0xffffffffu, incl, 31);
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
     }
-    if (lane == 0) tot[e] = carry;
+    if (sidx < nseg) row[sidx] = carry + incl - c;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
   }
-  __syncthreads();
-  int total = block_exclusive_scan(tot, E, warp_tot);
-  for (int e = threadIdx.x; e < E; e += P_THREADS) {
-    if (off64) off64[e] = tot[e];
-    if (off32) off32[e] = tot[e];
-  }
-  if (threadIdx.x == 0) {
-    if (off64) off64[E] = total;
-    if (off32) off32[E] = total;
-  }
+  if (lane == 0) totals[e] = carry;
 }
 
+// Every CTA turns the per-expert totals into offsets itself (E loads and a block scan); CTA 0 also
+// publishes them.  Then the segment is ranked and placed.
 template <bool IDS64>
 __global__ void __launch_bounds__(P_THREADS)
-permute_place(const void* __restrict__ ids, int64_t S, int E, const int32_t* __restrict__ seg_base,
-              const int32_t* __restrict__ off32, int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+permute_place(const void* __restrict__ ids, int64_t S, int E, int nseg, const int32_t* __restrict__ seg_base,
+              const int32_t* __restrict__ totals, int64_t* __restrict__ off64, int32_t* __restrict__ off32,
+              int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
   __shared__ int run[P_MAX_E];
-  for (int e = threadIdx.x; e < E; e += P_THREADS) run[e] = off32[e] + seg_base[(size_t)blockIdx.x * E + e];
+  __shared__ int warp_tot[P_THREADS / 32];
+  for (int e = threadIdx.x; e < E; e += P_THREADS) run[e] = totals[e];
+  __syncthreads();
+  const int total = block_exclusive_scan(run, E, warp_tot);
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e < E; e += P_THREADS) {
+      if (off64) off64[e] = run[e];
+      if (off32) off32[e] = run[e];
+    }
+    if (threadIdx.x == 0) {
+      if (off64) off64[E] = total;
+      if (off32) off32[E] = total;
+    }
+  }
+  for (int e = threadIdx.x; e < E; e += P_THREADS) run[e] += seg_base[(size_t)e * nseg + blockIdx.x];
   __syncthreads();
   const int64_t lo = (int64_t)blockIdx.x * P_SEG;
   place_segment<IDS64>(ids, lo, min(lo + (int64_t)P_SEG, S), E, run, perm, inv);
@@ -285,12 +290,14 @@ extern "C" int mq_permute_plan(const void* ids, int ids_are_64, int64_t T, int64
   if (!workspace || workspace_bytes < mq_permute_workspace_bytes(S, E)) return MQ_ERR_WORKSPACE_TOO_SMALL;
   const int nseg = (int)((S + P_SEG - 1) / P_SEG);
   int32_t* seg_hist = reinterpret_cast<int32_t*>(workspace);
-  int32_t* off32 = offsets32 ? offsets32 : seg_hist + (size_t)nseg * E;
+  int32_t* totals = seg_hist + (size_t)nseg * E;
   if (ids_are_64) permute_hist<true><<<nseg, P_THREADS, 0, st>>>(ids, S, (int)E, seg_hist);
   else permute_hist<false><<<nseg, P_THREADS, 0, st>>>(ids, S, (int)E, seg_hist);
-  permute_scan<<<1, P_THREADS, 0, st>>>(seg_hist, nseg, (int)E, offsets64, off32);
-  if (ids_are_64) permute_place<true><<<nseg, P_THREADS, 0, st>>>(ids, S, (int)E, seg_hist, off32, perm, inv);
-  else permute_place<false><<<nseg, P_THREADS, 0, st>>>(ids, S, (int)E, seg_hist, off32, perm, inv);
+  permute_scan<<<(unsigned)((E + P_THREADS / 32 - 1) / (P_THREADS / 32)), P_THREADS, 0, st>>>(seg_hist, nseg, (int)E, totals);
+  if (ids_are_64)
+    permute_place<true><<<nseg, P_THREADS, 0, st>>>(ids, S, (int)E, nseg, seg_hist, totals, offsets64, offsets32, perm, inv);
+  else
+    permute_place<false><<<nseg, P_THREADS, 0, st>>>(ids, S, (int)E, nseg, seg_hist, totals, offsets64, offsets32, perm, inv);
   return check_launch();
 }
 
