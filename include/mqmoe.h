@@ -145,6 +145,16 @@ int mq_grouped_swiglu(const void* a, const void* w_gate_up, const int32_t* offse
                       int64_t S, int64_t E, int64_t weight_period, int64_t I, int64_t H, int dtype,
                       void* h, int32_t* d_status, void* stream);
 
+/* The same with the permute gather fused in (moe_permute.py:30-31 + layers/moe.py:24-25): `x` is
+ * the UNPERMUTED [T,H] activations and row p of the expert-sorted order is x[perm[p] / top_k]; the
+ * rows are gathered inside the kernel, so the [T*top_k, H] copy is never written.
+ * bf16 only, H % 64 == 0, I % 128 == 0 (returns MQ_ERR_UNSUPPORTED_SHAPE otherwise: gather with
+ * mq_gather_rows and call mq_grouped_swiglu). */
+int mq_grouped_swiglu_gather(const void* x, const int32_t* perm, const void* w_gate_up,
+                             const int32_t* offsets, int64_t T, int64_t top_k, int64_t E,
+                             int64_t weight_period, int64_t I, int64_t H, int dtype,
+                             void* h, int32_t* d_status, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * W4A16 linear.  Replaces w4a16_gemm (mini_qwen/kernels/w4a16_gemm.py:8-15,194-247) and,
  * with E > 1, the per-expert calls LinearW4A16.forward makes from the expert loop

@@ -12,7 +12,8 @@ int grouped_gemm_generic_dispatch(const void* a, const void* w, const int32_t* o
 
 // tcgen05 kernel (bf16). Returns MQ_ERR_UNSUPPORTED_SHAPE when the shape is outside its cover.
 int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t period,
-                     int64_t N, int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st);
+                     int64_t N, int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st,
+                     const int32_t* perm, int64_t top_k);
 bool tc5_covers(int64_t S, int64_t E, int64_t N, int64_t Kd, bool swiglu);
 
 }  // namespace mq
@@ -47,7 +48,7 @@ static int grouped_common(const void* a, const void* w, const int32_t* offsets, 
   if (!a || !w || !offsets || !out) return MQ_ERR_INVALID_ARGUMENT;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == MQ_BF16 && tc5_covers(S, period, N, Kd, swiglu) && aligned16(a) && aligned16(w) && aligned16(out))
-    return grouped_gemm_tc5(a, w, offsets, S, E, period, N, Kd, swiglu, out, d_status, st);
+    return grouped_gemm_tc5(a, w, offsets, S, E, period, N, Kd, swiglu, out, d_status, st, nullptr, 1);
   return grouped_gemm_generic_dispatch(a, w, offsets, S, E, period, N, Kd, dtype, swiglu, out, st);
 }
 
@@ -61,4 +62,21 @@ extern "C" int mq_grouped_swiglu(const void* a, const void* w_gate_up, const int
                                  int64_t S, int64_t E, int64_t weight_period, int64_t I, int64_t H, int dtype,
                                  void* h, int32_t* d_status, void* stream) {
   return grouped_common(a, w_gate_up, offsets, S, E, weight_period, I, H, dtype, true, h, d_status, stream);
+}
+
+extern "C" int mq_grouped_swiglu_gather(const void* x, const int32_t* perm, const void* w_gate_up,
+                                        const int32_t* offsets, int64_t T, int64_t top_k, int64_t E,
+                                        int64_t weight_period, int64_t I, int64_t H, int dtype,
+                                        void* h, int32_t* d_status, void* stream) {
+  using namespace mq;
+  if (T < 0 || top_k <= 0 || E <= 0 || I <= 0 || H <= 0 || weight_period <= 0 || weight_period > E)
+    return MQ_ERR_INVALID_ARGUMENT;
+  const int64_t S = T * top_k;
+  if (dtype != MQ_BF16 || !tc5_covers(S, weight_period, I, H, true) || T >= ((int64_t)1 << 30))
+    return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (S == 0) return MQ_OK;
+  if (!x || !perm || !w_gate_up || !offsets || !h) return MQ_ERR_INVALID_ARGUMENT;
+  if (!aligned16(x) || !aligned16(w_gate_up) || !aligned16(h)) return MQ_ERR_INVALID_ARGUMENT;
+  return grouped_gemm_tc5(x, w_gate_up, offsets, S, E, weight_period, I, H, true, h, d_status,
+                          reinterpret_cast<cudaStream_t>(stream), perm, top_k);
 }

@@ -46,10 +46,12 @@ constexpr int BOX_TOK = 64;                     // token rows per TMA box
 constexpr int BOX_TOK_BYTES = BOX_TOK * BK * 2; // 8 KB
 constexpr int STAGE_BYTES = 2 * A_BYTES + B_BYTES;
 constexpr int EPI_WARPS = 8;
+constexpr int GATHER_WARPS = 4;                 // producer warps that gather token rows (fused-permute variant)
 constexpr int TR_PITCH = 64;                    // bytes per token row of a warp's 32x32 bf16 transpose block
 constexpr int TR_BYTES = 32 * TR_PITCH;         // per epilogue warp
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + EPI_WARPS * TR_BYTES;
 constexpr int TC5_THREADS = (2 + EPI_WARPS) * 32;
+constexpr int TC5_GATHER_THREADS = (2 + EPI_WARPS + GATHER_WARPS) * 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -89,6 +91,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// Makes this thread's completed shared-memory writes visible to the async proxy (the tensor core reads).
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -213,10 +225,16 @@ struct TileCursor {
   }
 };
 
-template <bool SWIGLU>
-__global__ void __launch_bounds__(TC5_THREADS, 1)
+// GATHER: the token operand is not read from expert-sorted rows but gathered from the unpermuted
+// activations x [T, Kd]: sorted row p is x[perm[p] / top_k].  Four extra producer warps copy the rows
+// with 16-byte cp.async into the 128-byte-swizzled layout the MMA expects (chunk c of row r lands at
+// chunk c ^ (r & 7)), one commit group per k-block; when a group has landed the thread fences towards
+// the async proxy and arrives on the stage's barrier.  Weights still come by TMA.
+template <bool SWIGLU, bool GATHER>
+__global__ void __launch_bounds__(GATHER ? TC5_GATHER_THREADS : TC5_THREADS, 1)
 grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                         const int32_t* __restrict__ offsets, int E, int period, int N, int Kd,
+                        const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ perm, int top_k,
                         __nv_bfloat16* __restrict__ out, int32_t* d_status) {
   // N: output columns.  SWIGLU: the weights hold 2N rows per expert (gate rows, then up rows).
   extern __shared__ uint8_t smem_raw[];
@@ -239,7 +257,10 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
   const int w_rows_per_expert = SWIGLU ? 2 * N : N;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), GATHER ? 1 + GATHER_WARPS * 32 : 1);
+      mbar_init(empty_bar(s), 1);
+    }
     mbar_init(tfull_bar, 1);
     mbar_init(tempty_bar, EPI_WARPS * 32);
     *abort_flag = 0;
@@ -271,7 +292,7 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         const int wrow1 = SWIGLU ? wbase + N + f0 : wbase + f0 + TM;
         const bool two = SWIGLU || (f0 + TM < N);
         const int nbox = (tl.n_mma + BOX_TOK - 1) / BOX_TOK;
-        const uint32_t tx = (uint32_t)((two ? 2 : 1) * A_BYTES + nbox * BOX_TOK_BYTES);
+        const uint32_t tx = (uint32_t)((two ? 2 : 1) * A_BYTES + (GATHER ? 0 : nbox * BOX_TOK_BYTES));
         for (int kb = 0; kb < KB && ok; ++kb) {
           ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, d_status);
           if (!ok) break;
@@ -281,8 +302,10 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
           mbar_expect_tx(full_bar(stage), tx);
           tma_load_2d(sa0, &map_w, full_bar(stage), kb * BK, wrow0);
           if (two) tma_load_2d(sa1, &map_w, full_bar(stage), kb * BK, wrow1);
-          for (int b = 0; b < nbox; ++b)
-            tma_load_2d(sb + b * BOX_TOK_BYTES, &map_x, full_bar(stage), kb * BK, tl.tok0 + b * BOX_TOK);
+          if (!GATHER) {
+            for (int b = 0; b < nbox; ++b)
+              tma_load_2d(sb + b * BOX_TOK_BYTES, &map_x, full_bar(stage), kb * BK, tl.tok0 + b * BOX_TOK);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -330,6 +353,50 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         umma_commit(tfull_bar);                   // accumulators complete
         acc_phase ^= 1u;
       }
+    }
+  } else if (GATHER && warp >= 2 + EPI_WARPS) {
+    // ------------------------------------------------------------------ gather producers (warps 10..13)
+    const int gt = threadIdx.x - (2 + EPI_WARPS) * 32;       // 0 .. 127
+    const int chunk = gt & 7;                                // 16-byte piece of a 128-byte row
+    const int rbase = gt >> 3;                               // rows rbase, rbase+16, ... of the tile
+    TileCursor cur(offsets, E, NWT);
+    int stage = 0, prev_stage = -1;
+    uint32_t phase = 0;
+    bool ok = true;
+    Tile tl;
+    for (int t = blockIdx.x; ok; t += gridDim.x) {
+      if (!cur.locate(t, tl)) break;
+      const __nv_bfloat16* src[TN_MAX / 16];
+#pragma unroll
+      for (int i = 0; i < TN_MAX / 16; ++i) {
+        // rows past the end of the expert repeat its last row: computed, never stored
+        const int p = min(tl.tok0 + rbase + 16 * i, tl.tok_end - 1);
+        src[i] = x + (size_t)(perm[p] / top_k) * Kd + chunk * 8;
+      }
+      const int nrow = tl.n_mma;                             // rows the MMA reads (multiple of 16)
+      for (int kb = 0; kb < KB && ok; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, d_status));
+        if (!ok) break;
+        const uint32_t sb = tiles_base + stage * STAGE_BYTES + 2 * A_BYTES;
+#pragma unroll
+        for (int i = 0; i < TN_MAX / 16; ++i) {
+          const int r = rbase + 16 * i;
+          if (r < nrow) cp_async16(sb + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4), src[i] + kb * BK);
+        }
+        cp_async_commit();
+        if (prev_stage >= 0) {                               // the previous k-block's rows have landed
+          cp_async_wait<1>();
+          fence_proxy_async();
+          mbar_arrive(full_bar(prev_stage));
+        }
+        prev_stage = stage;
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+    cp_async_wait<0>();
+    if (prev_stage >= 0 && ok) {
+      fence_proxy_async();
+      mbar_arrive(full_bar(prev_stage));
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
@@ -448,27 +515,36 @@ bool tc5_covers(int64_t S, int64_t E, int64_t N, int64_t Kd, bool swiglu) {
   return true;
 }
 
+// perm == nullptr: `a` holds the S expert-sorted rows.  perm != nullptr: `a` holds the unpermuted rows and
+// sorted row p is a[perm[p] / top_k], gathered inside the kernel.
 int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t period,
-                     int64_t N, int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st) {
+                     int64_t N, int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st,
+                     const int32_t* perm, int64_t top_k) {
   CUtensorMap map_x, map_w;
   const int64_t w_rows = period * (swiglu ? 2 * N : N);
-  if (!make_map(&map_x, a, (uint64_t)S, (uint64_t)Kd, BOX_TOK) ||
+  const bool gather = perm != nullptr;
+  // the gathering variant does not use map_x; it still needs a valid descriptor argument
+  if (!make_map(&map_x, a, (uint64_t)(gather ? BOX_TOK : S), (uint64_t)Kd, BOX_TOK) ||
       !make_map(&map_w, w, (uint64_t)w_rows, (uint64_t)Kd, TM))
     return MQ_ERR_DRIVER_ENTRY;
   const int64_t cols_per_tile = swiglu ? TM : 2 * TM;
   const int64_t nwt = (N + cols_per_tile - 1) / cols_per_tile;
   const int64_t tiles_max = ((S + TN_MAX - 1) / TN_MAX + E) * nwt;
   const int grid = (int)(tiles_max < sm_count() ? tiles_max : sm_count());
+  const __nv_bfloat16* xa = reinterpret_cast<const __nv_bfloat16*>(a);
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
   // the attribute is per device; setting it is cheap, so it is set on every call
-  if (swiglu) {
-    cudaFuncSetAttribute(grouped_gemm_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    grouped_gemm_tc5_kernel<true><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_x, map_w, offsets, (int)E, (int)period,
-        (int)N, (int)Kd, reinterpret_cast<__nv_bfloat16*>(out), d_status);
-  } else {
-    cudaFuncSetAttribute(grouped_gemm_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    grouped_gemm_tc5_kernel<false><<<grid, TC5_THREADS, SMEM_BYTES, st>>>(map_x, map_w, offsets, (int)E, (int)period,
-        (int)N, (int)Kd, reinterpret_cast<__nv_bfloat16*>(out), d_status);
-  }
+#define MQ_TC5_LAUNCH(SW, GA, THREADS)                                                                            \
+  do {                                                                                                            \
+    cudaFuncSetAttribute(grouped_gemm_tc5_kernel<SW, GA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); \
+    grouped_gemm_tc5_kernel<SW, GA><<<grid, THREADS, SMEM_BYTES, st>>>(map_x, map_w, offsets, (int)E, (int)period,  \
+        (int)N, (int)Kd, xa, perm, (int)top_k, o, d_status);                                                      \
+  } while (0)
+  if (swiglu && gather) MQ_TC5_LAUNCH(true, true, TC5_GATHER_THREADS);
+  else if (swiglu) MQ_TC5_LAUNCH(true, false, TC5_THREADS);
+  else if (gather) MQ_TC5_LAUNCH(false, true, TC5_GATHER_THREADS);
+  else MQ_TC5_LAUNCH(false, false, TC5_THREADS);
+#undef MQ_TC5_LAUNCH
   return check_launch();
 }
 

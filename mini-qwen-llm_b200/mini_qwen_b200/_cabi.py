@@ -32,6 +32,7 @@ PROTOTYPES = {
     "mq_unpermute_combine": (c_int, [_P, _I, _P, _P, _L, _L, _L, _P, _P]),
     "mq_grouped_gemm": (c_int, [_P, _P, _P, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
     "mq_grouped_swiglu": (c_int, [_P, _P, _P, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
+    "mq_grouped_swiglu_gather": (c_int, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
     "mq_w4a16_grouped_gemm": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P]),
     "mq_w4a16_grouped_swiglu": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P]),
     "mq_ep_share_counts": (c_int, [_P, _L, _L, _L, _P, _P]),

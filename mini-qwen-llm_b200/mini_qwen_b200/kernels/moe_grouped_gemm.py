@@ -73,3 +73,34 @@ def moe_grouped_swiglu(permuted_hidden: torch.Tensor, gate_up_weights: torch.Ten
     _cabi.check(rc, "mq_grouped_swiglu")
     _cabi.count_launches(1 if S else 0)
     return h
+
+
+def gather_swiglu_supported(hidden_states: torch.Tensor, gate_up_weights: torch.Tensor) -> bool:
+    """True when :func:`moe_grouped_swiglu_gather` covers these tensors (bf16, H % 64 == 0, I % 128 == 0)."""
+    E, I2, H = gate_up_weights.shape
+    return (hidden_states.dtype == torch.bfloat16 and gate_up_weights.dtype == torch.bfloat16
+            and H % 64 == 0 and (I2 // 2) % 128 == 0)
+
+
+def moe_grouped_swiglu_gather(hidden_states: torch.Tensor, perm: torch.Tensor, top_k: int,
+                              gate_up_weights: torch.Tensor, expert_offsets: torch.Tensor,
+                              status: torch.Tensor | None = None) -> torch.Tensor:
+    """:func:`moe_grouped_swiglu` on ``hidden_states[perm // top_k]`` without materialising the
+    permuted rows: the kernel gathers them itself.  ``hidden_states`` is the unpermuted [T, H]."""
+    _cabi.require_cuda(hidden_states, perm, gate_up_weights, expert_offsets)
+    E, I2, H = gate_up_weights.shape
+    x = hidden_states.contiguous()
+    T = x.shape[0]
+    S = perm.numel()
+    assert S == T * top_k and x.shape[1] == H
+    groups = expert_offsets.numel() - 1
+    h = torch.empty(S, I2 // 2, dtype=x.dtype, device=x.device)
+    if status is None:
+        status = _status_word(x.device)
+    rc = _cabi.load().mq_grouped_swiglu_gather(_cabi.ptr(x), _cabi.ptr(perm), _cabi.ptr(gate_up_weights),
+                                               _cabi.ptr(_offsets32(expert_offsets)), T, top_k, groups, E, I2 // 2, H,
+                                               _cabi.dtype_code(x), _cabi.ptr(h), _cabi.ptr(status),
+                                               _cabi.stream_ptr(x.device))
+    _cabi.check(rc, "mq_grouped_swiglu_gather")
+    _cabi.count_launches(1 if S else 0)
+    return h

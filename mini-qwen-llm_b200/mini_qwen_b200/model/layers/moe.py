@@ -15,7 +15,8 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ...kernels.moe_grouped_gemm import moe_grouped_gemm, moe_grouped_swiglu
+from ...kernels.moe_grouped_gemm import (gather_swiglu_supported, moe_grouped_gemm, moe_grouped_swiglu,
+                                          moe_grouped_swiglu_gather)
 from ...kernels.moe_permute import gather_rows, moe_permute_plan
 from ...kernels.moe_router import moe_router
 from ...kernels.moe_unpermute import unpermute_combine
@@ -180,6 +181,12 @@ class Qwen3MoEBlock(nn.Module):
         perm, inv, off32, _ = run("permute_plan", moe_permute_plan, ids32, E, want_int64_offsets=False)
         if self.ep_size > 1 and self.ep_mode == "p2p":
             return self._forward_peer(x2d, st, weights, perm, inv, off32, T, K, E).reshape(shape)
+        if self.ep_size == 1 and not st["w4"] and gather_swiglu_supported(x2d, st["w13"]):
+            # the gate/up kernel fetches the rows through the permutation itself: no permuted copy
+            status = self._status_word(x2d.device)
+            h = run("grouped_swiglu", moe_grouped_swiglu_gather, x2d, perm, K, st["w13"], off32, status=status)
+            out_perm = run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False, status=status)
+            return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K).reshape(shape)
         plan = None
         if self.ep_size > 1:
             all_counts = parallel.gather_counts(off32[1:] - off32[:-1], self.ep_group)

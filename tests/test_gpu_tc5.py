@@ -73,3 +73,21 @@ def test_tc5_rows_outside_experts_untouched():
     ref[10:150] = (a[10:150].float() @ w[0].float().T).to(torch.bfloat16)
     ref[150:280] = (a[150:280].float() @ w[1].float().T).to(torch.bfloat16)
     torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("T,K,E,I,H", [(64, 2, 4, 128, 64), (300, 4, 8, 256, 256), (1024, 8, 16, 768, 2048)])
+def test_tc5_swiglu_with_fused_gather(T, K, E, I, H):
+    """The gather-fused gate/up kernel (rows fetched through the permutation by producer warps) must
+    give the very bits of the two-step path (row gather, then the same kernel on contiguous rows)."""
+    from mini_qwen_b200.kernels import moe_grouped_swiglu_gather, moe_permute_plan
+    from mini_qwen_b200.kernels.moe_permute import gather_rows
+    g = torch.Generator().manual_seed(T + I)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    perm, inv, off32, _ = moe_permute_plan(ids, E, want_int64_offsets=False)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    fused = moe_grouped_swiglu_gather(x, perm, K, w13, off32, status=status)
+    assert status.item() == 0
+    two_step = moe_grouped_swiglu(gather_rows(x, perm, K), w13, off32)
+    assert torch.equal(fused, two_step)
