@@ -135,6 +135,17 @@ int mq_grouped_gemm(const void* a, const void* w, const int32_t* offsets,
                     int64_t S, int64_t E, int64_t weight_period, int64_t N, int64_t Kd, int dtype,
                     void* out, int32_t* d_status, void* stream);
 
+/* mq_grouped_gemm with one destination per group: the rows of group g are written from address
+ * group_out[g] on (row r of the group at group_out[g] + (r - offsets[g]) * N elements) instead of
+ * into one [S,N] tensor.  The addresses may lie in another GPU's memory (peer-mapped): expert
+ * parallelism uses this to send every expert output row back to the rank it came from out of the
+ * GEMM's own epilogue, so the transfer overlaps the remaining tiles.  No counterpart in the
+ * reference (it is single-GPU).  group_out: device array of E addresses, each 16-byte aligned.
+ * bf16, Kd % 64 == 0, N % 128 == 0 only (MQ_ERR_UNSUPPORTED_SHAPE otherwise). */
+int mq_grouped_gemm_scatter(const void* a, const void* w, const int32_t* offsets,
+                            const int64_t* group_out, int64_t S, int64_t E, int64_t weight_period,
+                            int64_t N, int64_t Kd, int dtype, int32_t* d_status, void* stream);
+
 /* Fused gate/up projection with SwiGLU. Replaces _ExpertMLP's first half
  * (mini_qwen/model/layers/moe.py:24-25) for all experts at once:
  *   h[s,:] = round(round(silu(round(a[s,:] . wg[e]^T))) * round(a[s,:] . wu[e]^T)),
@@ -190,7 +201,12 @@ int mq_w4a16_grouped_swiglu(const void* x,
  *
  * mq_ep_plan: all_counts int32 [G,E] (per-expert slot counts of every rank) ->
  *   send_base int32 [E]: row in the owner's receive buffer where this rank's rows of expert e start;
- *   seg_offsets int32 [E+1]: prefix sums of this rank's G*(E/G) receive groups.
+ *   seg_offsets int32 [E+1]: prefix sums of this rank's G*(E/G) receive groups;
+ *   return_base int64 [E] (optional, with peer_y_ptrs and row_bytes; NULL to skip): for receive group
+ *   g = (source s, local expert j), the address in rank s's output buffer of the row at which that
+ *   group starts in rank s's expert-sorted order.  Passed as group_out to mq_grouped_gemm_scatter,
+ *   it makes the down projection deliver every output row to the position it left from, so the
+ *   source finishes with a local mq_unpermute_combine instead of mq_ep_combine.
  * mq_ep_dispatch: fused permute + dispatch.  Row p of the expert-sorted order (token perm[p]/K of x)
  *   is written into the owner's receive buffer; slot_dst[p] = owner * cap_rows + row (or -1 and
  *   status bit 2 when the row would not fit in cap_rows).
@@ -207,7 +223,8 @@ int mq_ep_share_counts(const int32_t* offsets, int64_t E, int64_t G, int64_t ran
 int mq_ep_barrier(const uint64_t* peer_signal_ptrs, int32_t* epoch_counter, int64_t G, int64_t rank,
                   int32_t* d_status, void* stream);
 int mq_ep_plan(const int32_t* all_counts, int64_t G, int64_t rank, int64_t E,
-               int32_t* send_base, int32_t* seg_offsets, void* stream);
+               int32_t* send_base, int32_t* seg_offsets,
+               const uint64_t* peer_y_ptrs, int64_t row_bytes, int64_t* return_base, void* stream);
 int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, const int32_t* offsets,
                    const int32_t* send_base, int64_t S, int64_t K, int64_t H, int64_t E, int64_t G,
                    const uint64_t* peer_recv_ptrs, int64_t cap_rows, int32_t* slot_dst,

@@ -20,8 +20,20 @@ namespace {
 //   seg_offsets[] = prefix sums of this rank's own receive groups, (source, local expert) order
 __global__ void __launch_bounds__(256)
 ep_plan_kernel(const int32_t* __restrict__ all_counts, int G, int rank, int E,
-               int32_t* __restrict__ send_base, int32_t* __restrict__ seg_offsets) {
+               int32_t* __restrict__ send_base, int32_t* __restrict__ seg_offsets,
+               const uint64_t* __restrict__ peer_y, int64_t row_bytes, int64_t* __restrict__ return_base) {
   const int el = E / G;
+  // way back: the rows of receive group (s, j) are rows [P, P + count) of rank s's expert-sorted order,
+  // P = number of rank s's slots on experts before rank * el + j; their outputs go to that place in
+  // rank s's buffer
+  if (return_base != nullptr) {
+    for (int g = threadIdx.x; g < E; g += blockDim.x) {
+      const int s = g / el, j = g - s * el;
+      int64_t before = 0;
+      for (int e = 0; e < rank * el + j; ++e) before += all_counts[s * E + e];
+      return_base[g] = (int64_t)peer_y[s] + before * row_bytes;
+    }
+  }
   // destination-side bases: one thread per expert, serial prefix over the (source, local expert) groups
   // that precede (rank, e % el) on the owner of e.  G * el <= 1024 groups: a few hundred adds.
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -178,13 +190,16 @@ int launch_ep_combine(const uint64_t* peer_y, const float* weights, const int32_
 }  // namespace mq
 
 extern "C" int mq_ep_plan(const int32_t* all_counts, int64_t G, int64_t rank, int64_t E,
-                          int32_t* send_base, int32_t* seg_offsets, void* stream) {
+                          int32_t* send_base, int32_t* seg_offsets,
+                          const uint64_t* peer_y_ptrs, int64_t row_bytes, int64_t* return_base, void* stream) {
   using namespace mq;
   if (G <= 0 || E <= 0 || rank < 0 || rank >= G || E % G != 0) return MQ_ERR_INVALID_ARGUMENT;
   if (E > 1024) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (!all_counts || !send_base || !seg_offsets) return MQ_ERR_INVALID_ARGUMENT;
+  if (return_base != nullptr && (!peer_y_ptrs || row_bytes <= 0 || row_bytes % 16 != 0)) return MQ_ERR_INVALID_ARGUMENT;
   ep_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(all_counts, (int)G, (int)rank, (int)E,
-                                                                       send_base, seg_offsets);
+                                                                       send_base, seg_offsets, peer_y_ptrs,
+                                                                       row_bytes, return_base);
   return check_launch();
 }
 

@@ -47,9 +47,10 @@ constexpr int BOX_TOK_BYTES = BOX_TOK * BK * 2; // 8 KB
 constexpr int STAGE_BYTES = 2 * A_BYTES + B_BYTES;
 constexpr int EPI_WARPS = 8;
 constexpr int GATHER_WARPS = 4;                 // producer warps that gather token rows (fused-permute variant)
-constexpr int TR_PITCH = 64;                    // bytes per token row of a warp's 32x32 bf16 transpose block
-constexpr int TR_BYTES = 32 * TR_PITCH;         // per epilogue warp
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + EPI_WARPS * TR_BYTES;
+constexpr int STG_ROWS = 32;                    // token rows per epilogue chunk
+constexpr int STG_PITCH_MAX = 2 * TM * 2;       // bytes per staged token row: up to 256 bf16 output columns
+constexpr int STG_BYTES = STG_ROWS * STG_PITCH_MAX;   // per group of four epilogue warps
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + (EPI_WARPS / 4) * STG_BYTES;
 constexpr int TC5_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int TC5_GATHER_THREADS = (2 + EPI_WARPS + GATHER_WARPS) * 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
@@ -160,35 +161,26 @@ __device__ __forceinline__ uint32_t swiglu_pair(float g0, float g1, float u0, fl
   return *reinterpret_cast<const uint32_t*>(&o);
 }
 
-// Writes a warp's 32 (tokens) x 32 (output columns) block of bf16 values, held as one column per lane
-// (vals[j] = packed tokens 2j, 2j+1), to global memory as 64-byte row segments.  The block is transposed
-// through shared memory; on the way out 4 lanes share a token row (16 bytes each), so one store
-// instruction covers 8 full 64-byte segments.  dst points at column 0 of the block in token row 0;
-// rows >= valid_rows are not written.
-__device__ __forceinline__ void store_block_transposed(const uint32_t (&vals)[16], uint8_t* tbuf, int lane,
-                                                       __nv_bfloat16* dst, size_t row_stride, int valid_rows) {
+// Barrier among the four epilogue warps that drain the same 32-token chunks (ids 1 and 2; 0 is __syncthreads).
+__device__ __forceinline__ void epi_group_sync(int group) {
+  asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
+}
+
+// Puts a warp's 32 (tokens) x 32 (output columns) block of bf16 values, held as one column per lane
+// (vals[j] = packed tokens 2j, 2j+1), into the chunk's staging rows: stg + token * pitch + column * 2.
+__device__ __forceinline__ void stage_block(const uint32_t (&vals)[16], uint8_t* stg, int pitch, int col) {
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    *reinterpret_cast<uint16_t*>(tbuf + (2 * j) * TR_PITCH + 2 * lane) = (uint16_t)(vals[j] & 0xffffu);
-    *reinterpret_cast<uint16_t*>(tbuf + (2 * j + 1) * TR_PITCH + 2 * lane) = (uint16_t)(vals[j] >> 16);
+    *reinterpret_cast<uint16_t*>(stg + (2 * j) * pitch + 2 * col) = (uint16_t)(vals[j] & 0xffffu);
+    *reinterpret_cast<uint16_t*>(stg + (2 * j + 1) * pitch + 2 * col) = (uint16_t)(vals[j] >> 16);
   }
-  __syncwarp();
-  const int piece = lane & 3;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int row = 8 * i + (lane >> 2);
-    if (row < valid_rows) {
-      const uint4 v = *reinterpret_cast<const uint4*>(tbuf + row * TR_PITCH + piece * 16);
-      *reinterpret_cast<uint4*>(dst + (size_t)row * row_stride + piece * 8) = v;
-    }
-  }
-  __syncwarp();
 }
 
 // One tile of work.
 struct Tile {
   int expert;     // group index (weights: expert % period)
   int wt;         // weight tile index
+  int lo;         // first row of the group
   int tok0;       // first row of the token tile
   int tok_end;    // one past the last valid row (end of the tile or of the expert)
   int n_mma;      // MMA N: rows of the token tile rounded up to 16
@@ -212,6 +204,7 @@ struct TileCursor {
         const int tt = local / NWT;
         const int width = (((n + ntt - 1) / ntt) + 15) & ~15;     // balanced token tiles, multiple of 16
         tile.expert = e;
+        tile.lo = lo;
         tile.wt = local - tt * NWT;
         tile.tok0 = lo + tt * width;
         tile.tok_end = min(tile.tok0 + width, hi);
@@ -235,7 +228,10 @@ __global__ void __launch_bounds__(GATHER ? TC5_GATHER_THREADS : TC5_THREADS, 1)
 grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                         const int32_t* __restrict__ offsets, int E, int period, int N, int Kd,
                         const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ perm, int top_k,
-                        __nv_bfloat16* __restrict__ out, int32_t* d_status) {
+                        __nv_bfloat16* __restrict__ out, const int64_t* __restrict__ group_out, int32_t* d_status) {
+  // group_out == nullptr: row r of the input produces row r of `out`.  Otherwise the rows of group g are
+  // written from address group_out[g] on (row r of the group at + (r - offsets[g]) * N elements), which
+  // may be another GPU's memory: the epilogue's stores then travel over NVLink while later tiles compute.
   // N: output columns.  SWIGLU: the weights hold 2N rows per expert (gate rows, then up rows).
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -363,16 +359,25 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     int stage = 0, prev_stage = -1;
     uint32_t phase = 0;
     bool ok = true;
-    Tile tl;
-    for (int t = blockIdx.x; ok; t += gridDim.x) {
-      if (!cur.locate(t, tl)) break;
-      const __nv_bfloat16* src[TN_MAX / 16];
+    // The sorted positions of the NEXT tile are fetched while the current tile is copied, so that the
+    // dependent perm loads never sit between two k-blocks of the ring.
+    Tile tl, nx;
+    int slot[TN_MAX / 16], slot_nx[TN_MAX / 16];
+    auto fetch_slots = [&](const Tile& tile, int (&dst)[TN_MAX / 16]) {
 #pragma unroll
-      for (int i = 0; i < TN_MAX / 16; ++i) {
-        // rows past the end of the expert repeat its last row: computed, never stored
-        const int p = min(tl.tok0 + rbase + 16 * i, tl.tok_end - 1);
-        src[i] = x + (size_t)(perm[p] / top_k) * Kd + chunk * 8;
-      }
+      for (int i = 0; i < TN_MAX / 16; ++i)   // rows past the end of the expert repeat its last row: computed, never stored
+        dst[i] = perm[min(tile.tok0 + rbase + 16 * i, tile.tok_end - 1)];
+    };
+    int t = blockIdx.x;
+    bool have = cur.locate(t, tl);
+    if (have) fetch_slots(tl, slot);
+    while (have && ok) {
+      t += gridDim.x;
+      const bool have_nx = cur.locate(t, nx);
+      if (have_nx) fetch_slots(nx, slot_nx);
+      uint32_t src_off[TN_MAX / 16];           // element offset of this thread's piece of each row in x
+#pragma unroll
+      for (int i = 0; i < TN_MAX / 16; ++i) src_off[i] = (uint32_t)(slot[i] / top_k) * (uint32_t)Kd + chunk * 8;
       const int nrow = tl.n_mma;                             // rows the MMA reads (multiple of 16)
       for (int kb = 0; kb < KB && ok; ++kb) {
         ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, d_status));
@@ -381,7 +386,8 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
 #pragma unroll
         for (int i = 0; i < TN_MAX / 16; ++i) {
           const int r = rbase + 16 * i;
-          if (r < nrow) cp_async16(sb + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4), src[i] + kb * BK);
+          if (r < nrow)
+            cp_async16(sb + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4), x + src_off[i] + kb * BK);
         }
         cp_async_commit();
         if (prev_stage >= 0) {                               // the previous k-block's rows have landed
@@ -392,6 +398,10 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         prev_stage = stage;
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
+      have = have_nx;
+      tl = nx;
+#pragma unroll
+      for (int i = 0; i < TN_MAX / 16; ++i) slot[i] = slot_nx[i];
     }
     cp_async_wait<0>();
     if (prev_stage >= 0 && ok) {
@@ -400,52 +410,88 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // Warps 2..5 drain the even 32-token chunks of a tile, warps 6..9 the odd ones.  The four warps of
+    // a group hold one TMEM lane quadrant (32 output columns) each; they put their blocks side by side
+    // into the group's staging rows, then every warp writes whole rows: 256 (SwiGLU) or 512 bytes of
+    // one token row per store instruction, which is what a remote destination over NVLink wants.
     TileCursor cur(offsets, E, NWT);
     const int quad = warp & 3;                     // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;              // which 32-token chunks (even / odd) this warp drains
-    uint8_t* tbuf = bar_mem + 256 + (warp - 2) * TR_BYTES;
+    const int half = (warp - 2) >> 2;              // which 32-token chunks (even / odd) this group drains
+    const int wig = (warp - 2) & 3;                // warp within the group: stores rows 8*wig .. 8*wig+7
+    uint8_t* stg = bar_mem + 256 + half * STG_BYTES;
+    volatile int* group_go = reinterpret_cast<volatile int*>(bar_mem + 8 * (2 * STAGES + 2) + 16) + half;
+    const int pitch = cols_per_tile * 2;
     uint32_t acc_phase = 0;
-    bool ok = true;
     Tile tl;
-    for (int t = blockIdx.x; ok; t += gridDim.x) {
+    for (int t = blockIdx.x;; t += gridDim.x) {
       if (!cur.locate(t, tl)) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar, acc_phase, abort_flag, d_status));
-      if (!ok) break;
+      mbar_wait(tfull_bar, acc_phase, abort_flag, d_status);
+      // the four warps must take the same decision, or the group barriers below would never fill
+      epi_group_sync(half);
+      if (wig == 0 && lane == 0) *group_go = (*abort_flag == 0);
+      epi_group_sync(half);
+      if (*group_go == 0) break;
       tc_fence_after();
       const int f0 = tl.wt * cols_per_tile;
       const bool two = SWIGLU || (f0 + TM < N);
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
       const int ntok = tl.tok_end - tl.tok0;
+      __nv_bfloat16* out_base = group_out == nullptr ? out
+          : reinterpret_cast<__nv_bfloat16*>(group_out[tl.expert]) - (size_t)tl.lo * N;
       for (int c = half * 32; c < tl.n_mma; c += 64) {
         // lane = output column quad*32+lane of the sub-tile; registers = 32 consecutive tokens
         uint32_t r0[32], r1[32], packed[16];
         tmem_ld32(taddr + c, r0);
         if (two) tmem_ld32(taddr + TN_MAX + c, r1);
         tmem_ld_wait();
-        const int valid = ntok - c;                    // token rows of this chunk that exist
-        __nv_bfloat16* oblk = out + (size_t)(tl.tok0 + c) * N + f0 + quad * 32;
         if (SWIGLU) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             packed[j] = swiglu_pair(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]),
                                     __uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-          store_block_transposed(packed, tbuf, lane, oblk, (size_t)N, valid);
+          stage_block(packed, stg, pitch, quad * 32 + lane);
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
             packed[j] = *reinterpret_cast<const uint32_t*>(&p);
           }
-          store_block_transposed(packed, tbuf, lane, oblk, (size_t)N, valid);
+          stage_block(packed, stg, pitch, quad * 32 + lane);
           if (two) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
               packed[j] = *reinterpret_cast<const uint32_t*>(&p);
             }
-            store_block_transposed(packed, tbuf, lane, oblk + TM, (size_t)N, valid);
+            stage_block(packed, stg, pitch, TM + quad * 32 + lane);
           }
         }
+        epi_group_sync(half);                          // the chunk's rows are complete
+        const int valid = ntok - c;                    // token rows of this chunk that exist
+        __nv_bfloat16* orow = out_base + (size_t)(tl.tok0 + c) * N + f0;
+        if (SWIGLU) {
+          // 16 lanes cover a 256-byte row: two rows per instruction
+          const int piece = lane & 15;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int row = 8 * wig + 2 * i + (lane >> 4);
+            if (row < valid) {
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + row * pitch + piece * 16);
+              *reinterpret_cast<uint4*>(orow + (size_t)row * N + piece * 8) = v;
+            }
+          }
+        } else {
+          const bool col_ok = two || lane < 16;        // the last weight tile may hold one sub-tile only
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = 8 * wig + i;
+            if (row < valid && col_ok) {
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + row * pitch + lane * 16);
+              *reinterpret_cast<uint4*>(orow + (size_t)row * N + lane * 8) = v;
+            }
+          }
+        }
+        epi_group_sync(half);                          // the staging rows may be overwritten
       }
       tc_fence_before();
       mbar_arrive(tempty_bar);
@@ -519,7 +565,7 @@ bool tc5_covers(int64_t S, int64_t E, int64_t N, int64_t Kd, bool swiglu) {
 // sorted row p is a[perm[p] / top_k], gathered inside the kernel.
 int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t period,
                      int64_t N, int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st,
-                     const int32_t* perm, int64_t top_k) {
+                     const int32_t* perm, int64_t top_k, const int64_t* group_out) {
   CUtensorMap map_x, map_w;
   const int64_t w_rows = period * (swiglu ? 2 * N : N);
   const bool gather = perm != nullptr;
@@ -538,7 +584,7 @@ int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64
   do {                                                                                                            \
     cudaFuncSetAttribute(grouped_gemm_tc5_kernel<SW, GA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); \
     grouped_gemm_tc5_kernel<SW, GA><<<grid, THREADS, SMEM_BYTES, st>>>(map_x, map_w, offsets, (int)E, (int)period,  \
-        (int)N, (int)Kd, xa, perm, (int)top_k, o, d_status);                                                      \
+        (int)N, (int)Kd, xa, perm, (int)top_k, o, group_out, d_status);                                                     \
   } while (0)
   if (swiglu && gather) MQ_TC5_LAUNCH(true, true, TC5_GATHER_THREADS);
   else if (swiglu) MQ_TC5_LAUNCH(true, false, TC5_THREADS);

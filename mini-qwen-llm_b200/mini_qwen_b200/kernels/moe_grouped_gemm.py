@@ -79,7 +79,7 @@ def gather_swiglu_supported(hidden_states: torch.Tensor, gate_up_weights: torch.
     """True when :func:`moe_grouped_swiglu_gather` covers these tensors (bf16, H % 64 == 0, I % 128 == 0)."""
     E, I2, H = gate_up_weights.shape
     return (hidden_states.dtype == torch.bfloat16 and gate_up_weights.dtype == torch.bfloat16
-            and H % 64 == 0 and (I2 // 2) % 128 == 0)
+            and H % 64 == 0 and (I2 // 2) % 128 == 0 and hidden_states.numel() < 2 ** 32)
 
 
 def moe_grouped_swiglu_gather(hidden_states: torch.Tensor, perm: torch.Tensor, top_k: int,
@@ -104,3 +104,30 @@ def moe_grouped_swiglu_gather(hidden_states: torch.Tensor, perm: torch.Tensor, t
     _cabi.check(rc, "mq_grouped_swiglu_gather")
     _cabi.count_launches(1 if S else 0)
     return h
+
+
+def scatter_gemm_supported(rows: torch.Tensor, expert_weights: torch.Tensor) -> bool:
+    """True when :func:`moe_grouped_gemm_scatter` covers these tensors (bf16, K % 64 == 0, N % 128 == 0)."""
+    E, N, Kd = expert_weights.shape
+    return (rows.dtype == torch.bfloat16 and expert_weights.dtype == torch.bfloat16
+            and Kd % 64 == 0 and N % 128 == 0)
+
+
+def moe_grouped_gemm_scatter(rows: torch.Tensor, expert_weights: torch.Tensor, expert_offsets: torch.Tensor,
+                             group_out: torch.Tensor, status: torch.Tensor | None = None) -> None:
+    """:func:`moe_grouped_gemm` whose output rows go to one destination per group: group g's rows are
+    written from address ``group_out[g]`` (int64 device addresses, possibly in a peer GPU's memory) on.
+    Nothing is returned; the caller owns the destination buffers and the ordering with their readers."""
+    _cabi.require_cuda(rows, expert_weights, expert_offsets, group_out)
+    E, N, Kd = expert_weights.shape
+    a = rows.contiguous()
+    S = a.shape[0]
+    groups = expert_offsets.numel() - 1
+    assert group_out.dtype == torch.int64 and group_out.numel() == groups and a.shape[1] == Kd
+    if status is None:
+        status = _status_word(a.device)
+    rc = _cabi.load().mq_grouped_gemm_scatter(_cabi.ptr(a), _cabi.ptr(expert_weights),
+                                              _cabi.ptr(_offsets32(expert_offsets)), _cabi.ptr(group_out), S, groups, E,
+                                              N, Kd, _cabi.dtype_code(a), _cabi.ptr(status), _cabi.stream_ptr(a.device))
+    _cabi.check(rc, "mq_grouped_gemm_scatter")
+    _cabi.count_launches(1 if S else 0)

@@ -15,8 +15,8 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ...kernels.moe_grouped_gemm import (gather_swiglu_supported, moe_grouped_gemm, moe_grouped_swiglu,
-                                          moe_grouped_swiglu_gather)
+from ...kernels.moe_grouped_gemm import (gather_swiglu_supported, moe_grouped_gemm, moe_grouped_gemm_scatter,
+                                          moe_grouped_swiglu, moe_grouped_swiglu_gather, scatter_gemm_supported)
 from ...kernels.moe_permute import gather_rows, moe_permute_plan
 from ...kernels.moe_router import moe_router
 from ...kernels.moe_unpermute import unpermute_combine
@@ -69,6 +69,9 @@ class Qwen3MoEBlock(nn.Module):
         # "nccl": materialise, then torch.distributed all-to-all (any backend; one host sync per call)
         self.ep_mode = ep_mode
         self.ep_max_tokens = ep_max_tokens     # most tokens per rank and call (sizes the peer buffers)
+        # "fused": the down projection writes its rows into the source ranks' buffers itself;
+        # "pull": the combine kernel reads them from the owners (the only way for W4A16 experts)
+        self.ep_return = "fused"
         self._peer = None
         self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
         self.ep_rank = 0 if ep_group is None else torch.distributed.get_rank(ep_group)
@@ -242,9 +245,21 @@ class Qwen3MoEBlock(nn.Module):
                              f"rank; got {T} of {x2d.dtype} (pass ep_max_tokens at construction)")
         all_counts = run("share_counts", peer.share_counts, off32)
         run("rank_barrier", peer.rank_barrier)
-        send_base, seg = run("ep_plan", peer.plan, all_counts)
+        # bf16 experts on the tcgen05 kernel send their output rows home from the down projection's own
+        # epilogue (NVLink stores under the remaining tiles); other layers are read back by the combine
+        fused_return = (not st["w4"]) and scatter_gemm_supported(peer.recv_rows(), st["w2"]) \
+            and self.ep_return == "fused"
+        send_base, seg, ret = run("ep_plan", peer.plan, all_counts, fused_return)
         slot_dst = run("dispatch", peer.dispatch, x2d, perm, off32, send_base, K, E)
         run("rank_barrier", peer.rank_barrier)
+        if fused_return:
+            status = self._status_word(x2d.device)
+            h = run("grouped_swiglu", moe_grouped_swiglu, peer.recv_rows(), st["w13"], seg, zero_init=False,
+                    status=status)
+            run("grouped_down", moe_grouped_gemm_scatter, h, st["w2"], seg, ret, status=status)
+            run("rank_barrier", peer.rank_barrier)
+            # every row of this rank's sorted order is back in its own buffer
+            return run("unpermute_combine", unpermute_combine, peer.y_rows()[:T * K], weights, inv, T, K)
         self._experts(st, peer.recv_rows(), seg, out=peer.y_rows())
         run("rank_barrier", peer.rank_barrier)
         return run("combine", peer.combine, weights, inv, slot_dst, T, K)

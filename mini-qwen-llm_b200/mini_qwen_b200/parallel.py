@@ -162,17 +162,25 @@ class PeerExchange:
         c.count_launches(1)
         return self._counts.view(self.world, E)
 
-    def plan(self, all_counts: torch.Tensor):
-        """Device-side plan (no host sync): (send_base int32 [E], seg_offsets int32 [E+1])."""
+    def plan(self, all_counts: torch.Tensor, with_return: bool = False):
+        """Device-side plan (no host sync): (send_base int32 [E], seg_offsets int32 [E+1], return_base).
+
+        ``return_base`` (int64 [E], only ``with_return``) holds, for every receive group (source, local
+        expert), the address in the SOURCE's output buffer where that group's rows sit in the source's
+        expert-sorted order: the down projection writes its output rows there itself."""
         G, E = all_counts.shape
         dev = all_counts.device
         send_base = torch.empty(E, dtype=torch.int32, device=dev)
         seg = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        ret = torch.empty(E, dtype=torch.int64, device=dev) if with_return else None
         c = self._cabi
-        rc = c.load().mq_ep_plan(c.ptr(all_counts), G, self.rank, E, c.ptr(send_base), c.ptr(seg), c.stream_ptr(dev))
+        row_bytes = self.hidden * self.y.element_size()
+        rc = c.load().mq_ep_plan(c.ptr(all_counts), G, self.rank, E, c.ptr(send_base), c.ptr(seg),
+                                 c.ptr(self.y_ptrs) if with_return else None, row_bytes,
+                                 c.ptr(ret) if with_return else None, c.stream_ptr(dev))
         c.check(rc, "mq_ep_plan")
         c.count_launches(1)
-        return send_base, seg
+        return send_base, seg, ret
 
     def dispatch(self, x: torch.Tensor, perm, off32, send_base, top_k: int, num_experts: int) -> torch.Tensor:
         """Fused permute + dispatch; returns slot_dst int32 [S] (owner * cap_rows + row)."""

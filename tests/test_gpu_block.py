@@ -203,3 +203,24 @@ def test_block_restacks_after_module_swap_and_move():
     # fp32 -> bf16 conversion re-creates the stacks
     blk16 = blk.to(torch.bfloat16)
     assert blk16(x.to(torch.bfloat16)).dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("w4", [False, True])
+def test_block_forward_captured_in_a_cuda_graph(w4):
+    """The forward pass has no host synchronisation, so it captures; replays give the eager bits, also
+    after the input buffer's content changes (routing is recomputed inside the graph)."""
+    from mini_qwen_b200.graph import CapturedForward
+    if w4:
+        lay = cases.config3()
+        blk, x = w4_block(lay), lay.x[:16].to(DEV)
+    else:
+        lay = cases.config4()
+        blk, x = dense_block(lay), lay.x.to(DEV)
+    eager = blk(x).clone()
+    cap = CapturedForward(blk, x)
+    assert cap.launches >= 5
+    assert torch.equal(cap.replay(), eager)
+    x2 = torch.roll(x, 3, dims=0).contiguous()
+    cap.x.copy_(x2)
+    assert torch.equal(cap.replay(), blk(x2))
+    blk.check_status()

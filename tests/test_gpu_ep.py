@@ -74,6 +74,17 @@ def _worker(rank, world, port, w4, mode):
         assert torch.equal(blk(x), out)                      # deterministic across calls
         if mode == "p2p":
             blk._peer.check_status()                          # no receive-buffer overflow
+            # the down projection delivering its rows itself and the combine fetching them give the same bits
+            blk.ep_return = "pull"
+            assert torch.equal(blk(x), out)
+            blk.ep_return = "fused"
+            assert torch.equal(blk(x), out)
+            blk.check_status()
+            from mini_qwen_b200.graph import CapturedForward
+            cap = CapturedForward(blk, x)                     # collective: every rank captures and replays
+            assert torch.equal(cap.replay(), out)
+            assert torch.equal(cap.replay(), out)
+            blk.check_status()
             out_small = blk(x[:17])                          # fewer tokens than the buffers were sized for
             assert out_small.shape == (17, H)
     finally:

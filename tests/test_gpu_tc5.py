@@ -91,3 +91,32 @@ def test_tc5_swiglu_with_fused_gather(T, K, E, I, H):
     assert status.item() == 0
     two_step = moe_grouped_swiglu(gather_rows(x, perm, K), w13, off32)
     assert torch.equal(fused, two_step)
+
+
+@pytest.mark.parametrize("counts,N,Kd", [([5, 0, 130, 17], 128, 64), ([260, 31, 0, 300, 1, 90], 256, 512),
+                                         ([700, 3, 256, 255, 257, 0, 16, 48], 2048, 768)])
+def test_tc5_scatter_gemm_writes_each_group_at_its_own_address(counts, N, Kd):
+    """Per-group destinations: the rows of every group land from the group's own address on (groups placed
+    in reverse order in one buffer, with a guard row between them), with the bits of the plain call."""
+    from mini_qwen_b200.kernels.moe_grouped_gemm import moe_grouped_gemm_scatter
+    E = len(counts)
+    S = sum(counts)
+    g = torch.Generator().manual_seed(S + N)
+    a = torch.randn(S, Kd, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(E, N, Kd, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    off = offsets_from_counts(counts).to(torch.int32).to(DEV)
+    plain = moe_grouped_gemm(a, w, off)
+    buf = torch.full((S + E, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    starts, row = [0] * E, 0
+    for e in reversed(range(E)):
+        starts[e] = row
+        row += counts[e] + 1                                   # one guard row after every group
+    addr = torch.tensor([buf.data_ptr() + s * N * 2 for s in starts], dtype=torch.int64, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    moe_grouped_gemm_scatter(a, w, off, addr, status=status)
+    assert status.item() == 0
+    lo = 0
+    for e in range(E):
+        assert torch.equal(buf[starts[e]:starts[e] + counts[e]], plain[lo:lo + counts[e]])
+        assert bool((buf[starts[e] + counts[e]] == 7.0).all())          # guard row untouched
+        lo += counts[e]
