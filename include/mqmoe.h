@@ -158,7 +158,9 @@ int mq_grouped_swiglu(const void* a, const void* w_gate_up, const int32_t* offse
 
 /* The same with the permute gather fused in (moe_permute.py:30-31 + layers/moe.py:24-25): `x` is
  * the UNPERMUTED [T,H] activations and row p of the expert-sorted order is x[perm[p] / top_k]; the
- * rows are gathered inside the kernel, so the [T*top_k, H] copy is never written.
+ * rows are gathered inside the kernel, so the [T*top_k, H] copy is never written.  The slot count is
+ * offsets[E] and need not be T*top_k: with top_k = 1, perm is a table of row numbers into x (the
+ * expert-parallel receive buffer and its slot table).  Every perm[p]/top_k read must be < T.
  * bf16 only, H % 64 == 0, I % 128 == 0 (returns MQ_ERR_UNSUPPORTED_SHAPE otherwise: gather with
  * mq_gather_rows and call mq_grouped_swiglu). */
 int mq_grouped_swiglu_gather(const void* x, const int32_t* perm, const void* w_gate_up,
@@ -229,6 +231,22 @@ int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, const int32_t*
                    const int32_t* send_base, int64_t S, int64_t K, int64_t H, int64_t E, int64_t G,
                    const uint64_t* peer_recv_ptrs, int64_t cap_rows, int32_t* slot_dst,
                    int32_t* d_status, void* stream);
+/* Dispatch that sends a token row once per destination RANK instead of once per slot (a token with
+ * several experts on one GPU crosses NVLink once).  G <= 8.
+ * mq_ep_unique_rows: topk_ids int32 [T,K] -> uniq int32 [T,G]: index of token t among this rank's
+ *   tokens that have an expert on rank d, in token order, or -1 when it has none there.
+ * mq_ep_dispatch_unique: row t goes to row rank*src_stride + uniq[t,d] of every rank d that needs it
+ *   (T <= src_stride, G*src_stride <= cap_rows), and every slot's row number goes to its place in the
+ *   owner's slot table peer_ridx_ptrs[d] (int32 [cap_rows], (source, local expert) order, the order
+ *   seg_offsets describes).  The owner runs mq_grouped_swiglu_gather with x = its receive buffer,
+ *   perm = its slot table, top_k = 1.  slot_dst as in mq_ep_dispatch. */
+int mq_ep_unique_rows(const int32_t* topk_ids, int64_t T, int64_t K, int64_t E, int64_t G,
+                      int32_t* uniq, void* stream);
+int mq_ep_dispatch_unique(const void* x, int dtype, const int32_t* uniq, const int32_t* perm,
+                          const int32_t* offsets, const int32_t* send_base, int64_t T, int64_t K,
+                          int64_t H, int64_t E, int64_t G, int64_t rank, int64_t src_stride,
+                          const uint64_t* peer_recv_ptrs, const uint64_t* peer_ridx_ptrs,
+                          int64_t cap_rows, int32_t* slot_dst, int32_t* d_status, void* stream);
 int mq_ep_combine(const uint64_t* peer_y_ptrs, int dtype, const float* weights, const int32_t* inv,
                   const int32_t* slot_dst, int64_t T, int64_t K, int64_t H, int64_t cap_rows,
                   void* out, void* stream);

@@ -127,6 +127,105 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm
   for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
 }
 
+// ---- dispatch with one copy per (token, destination rank) instead of one per slot.
+// A token with several of its K experts on the same GPU needs its row there once.  uniq[t, d] is the
+// index of token t among this rank's tokens that have at least one expert on rank d (token order), or
+// -1; the row travels to row rank * src_stride + uniq[t, d] of rank d's receive buffer, and every
+// slot carries only that row number (4 bytes) to its place in the (source, local expert) order.  The
+// gate/up kernel of the owner then gathers its rows through those numbers.
+constexpr int EP_MAX_G = 8;
+
+__global__ void __launch_bounds__(1024)
+ep_unique_rows_kernel(const int32_t* __restrict__ ids, int T, int K, int el, int G, int32_t* __restrict__ uniq) {
+  __shared__ int s_warp[32][EP_MAX_G];
+  __shared__ int s_carry[EP_MAX_G];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < EP_MAX_G) s_carry[threadIdx.x] = 0;
+  __syncthreads();
+  for (int t0 = 0; t0 < T; t0 += 1024) {                // one token per thread and pass
+    const int t = t0 + threadIdx.x;
+    unsigned mask = 0;
+    if (t < T)
+      for (int k = 0; k < K; ++k) mask |= 1u << (ids[(int64_t)t * K + k] / el);
+    int before[EP_MAX_G];
+#pragma unroll
+    for (int d = 0; d < EP_MAX_G; ++d) {
+      const unsigned votes = __ballot_sync(0xffffffffu, (mask >> d) & 1u);
+      before[d] = __popc(votes & ((1u << lane) - 1u));
+      if (lane == 0) s_warp[warp][d] = __popc(votes);
+    }
+    __syncthreads();
+    if (warp == 0) {                                    // exclusive scan of the 32 warp totals, per destination
+#pragma unroll
+      for (int d = 0; d < EP_MAX_G; ++d) {
+        const int v = s_warp[lane][d];
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += up;
+        }
+        s_warp[lane][d] = s_carry[d] + incl - v;
+        __syncwarp();
+        if (lane == 31) s_carry[d] += incl;
+      }
+    }
+    __syncthreads();
+    if (t < T)
+      for (int d = 0; d < G; ++d)
+        uniq[(int64_t)t * G + d] = ((mask >> d) & 1u) ? s_warp[warp][d] + before[d] : -1;
+    __syncthreads();
+  }
+}
+
+// Blocks [0, row_blocks): one warp per token, the row is read once and stored to every rank that needs it.
+// Blocks after: one thread per expert-sorted slot, the slot's row number goes to its owner.
+__global__ void __launch_bounds__(256)
+ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ uniq,
+                          const int32_t* __restrict__ perm, const int32_t* __restrict__ offsets,
+                          const int32_t* __restrict__ send_base, int T, int64_t S, int K, int vec_per_row, int E,
+                          int el, int G, int rank, int src_stride, int row_blocks,
+                          const uint64_t* __restrict__ peer_recv, const uint64_t* __restrict__ peer_ridx,
+                          int64_t cap_rows, int32_t* __restrict__ slot_dst, int32_t* __restrict__ status) {
+  if ((int)blockIdx.x < row_blocks) {
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const int lane = threadIdx.x & 31;
+    const int mine = lane < G ? uniq[(int64_t)t * G + lane] : -1;
+    uint4* dst[EP_MAX_G];
+#pragma unroll
+    for (int d = 0; d < EP_MAX_G; ++d) {
+      const int u = __shfl_sync(0xffffffffu, mine, d);
+      dst[d] = u < 0 ? nullptr
+                     : reinterpret_cast<uint4*>(peer_recv[d]) + ((int64_t)rank * src_stride + u) * vec_per_row;
+    }
+    const uint4* src = x + (int64_t)t * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      const uint4 val = __ldg(src + v);
+#pragma unroll
+      for (int d = 0; d < EP_MAX_G; ++d)
+        if (dst[d] != nullptr) dst[d][v] = val;
+    }
+    return;
+  }
+  const int64_t p = (int64_t)(blockIdx.x - row_blocks) * 256 + threadIdx.x;
+  if (p >= S) return;
+  int lo = 0, hi = E;                       // expert of sorted position p: offsets[lo] <= p < offsets[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (offsets[mid] <= (int)p) lo = mid; else hi = mid;
+  }
+  const int e = lo, d = e / el;
+  const int64_t row = (int64_t)send_base[e] + (p - offsets[e]);
+  if (row >= cap_rows) {                    // slot table of the owner too small for this routing
+    atomicOr(status, 2);
+    slot_dst[p] = -1;
+    return;
+  }
+  slot_dst[p] = (int32_t)(d * cap_rows + row);
+  reinterpret_cast<int32_t*>(peer_ridx[d])[row] = rank * src_stride + uniq[(int64_t)(perm[p] / K) * G + d];
+}
+
 // out[t,:] = cast(sum_k w[t,k] * float(y_on_owner[slot row, :])), fp32 multiply then add, k ascending.
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -251,4 +350,44 @@ extern "C" int mq_ep_combine(const uint64_t* peer_y_ptrs, int dtype, const float
   if (dtype == MQ_F32) return launch_ep_combine<float>(peer_y_ptrs, weights, inv, slot_dst, T, (int)K, H, cap_rows, out, st);
   if (dtype == MQ_BF16) return launch_ep_combine<__nv_bfloat16>(peer_y_ptrs, weights, inv, slot_dst, T, (int)K, H, cap_rows, out, st);
   return launch_ep_combine<__half>(peer_y_ptrs, weights, inv, slot_dst, T, (int)K, H, cap_rows, out, st);
+}
+
+extern "C" int mq_ep_unique_rows(const int32_t* topk_ids, int64_t T, int64_t K, int64_t E, int64_t G,
+                                 int32_t* uniq, void* stream) {
+  using namespace mq;
+  if (T < 0 || K <= 0 || E <= 0 || G <= 0 || E % G != 0) return MQ_ERR_INVALID_ARGUMENT;
+  if (G > EP_MAX_G || T >= ((int64_t)1 << 31) / (K > G ? K : G)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (T == 0) return MQ_OK;
+  if (!topk_ids || !uniq) return MQ_ERR_INVALID_ARGUMENT;
+  ep_unique_rows_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(topk_ids, (int)T, (int)K,
+                                                                                (int)(E / G), (int)G, uniq);
+  return check_launch();
+}
+
+extern "C" int mq_ep_dispatch_unique(const void* x, int dtype, const int32_t* uniq, const int32_t* perm,
+                                     const int32_t* offsets, const int32_t* send_base, int64_t T, int64_t K,
+                                     int64_t H, int64_t E, int64_t G, int64_t rank, int64_t src_stride,
+                                     const uint64_t* peer_recv_ptrs, const uint64_t* peer_ridx_ptrs,
+                                     int64_t cap_rows, int32_t* slot_dst, int32_t* d_status, void* stream) {
+  using namespace mq;
+  if (T < 0 || K <= 0 || H <= 0 || E <= 0 || G <= 0 || E % G != 0 || rank < 0 || rank >= G || !valid_dtype(dtype))
+    return MQ_ERR_INVALID_ARGUMENT;
+  if (G > EP_MAX_G || cap_rows <= 0 || G * cap_rows >= ((int64_t)1 << 31) || T * K >= ((int64_t)1 << 31))
+    return MQ_ERR_UNSUPPORTED_SHAPE;
+  // every source owns src_stride rows of every receive buffer
+  if (T > src_stride || G * src_stride > cap_rows) return MQ_ERR_INVALID_ARGUMENT;
+  const int64_t row_bytes = H * (int64_t)dtype_size(dtype);
+  if (row_bytes % 16 != 0) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (T == 0) return MQ_OK;
+  if (!x || !uniq || !perm || !offsets || !send_base || !peer_recv_ptrs || !peer_ridx_ptrs || !slot_dst || !d_status)
+    return MQ_ERR_INVALID_ARGUMENT;
+  if (!aligned16(x)) return MQ_ERR_INVALID_ARGUMENT;
+  const int64_t S = T * K;
+  const int row_blocks = (int)((T + 7) / 8);
+  const int64_t blocks = row_blocks + (S + 255) / 256;
+  ep_dispatch_unique_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(x), uniq, perm, offsets, send_base, (int)T, S, (int)K, (int)(row_bytes / 16),
+      (int)E, (int)(E / G), (int)G, (int)rank, (int)src_stride, row_blocks, peer_recv_ptrs, peer_ridx_ptrs,
+      cap_rows, slot_dst, d_status);
+  return check_launch();
 }

@@ -576,7 +576,9 @@ int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64
   const int64_t cols_per_tile = swiglu ? TM : 2 * TM;
   const int64_t nwt = (N + cols_per_tile - 1) / cols_per_tile;
   const int64_t tiles_max = ((S + TN_MAX - 1) / TN_MAX + E) * nwt;
-  const int grid = (int)(tiles_max < sm_count() ? tiles_max : sm_count());
+  // gathering: the number of slots is offsets[E], known only on the device (it is not T * top_k when the
+  // rows are a receive buffer addressed through a slot table), so the grid is not trimmed
+  const int grid = (int)(!gather && tiles_max < sm_count() ? tiles_max : sm_count());
   const __nv_bfloat16* xa = reinterpret_cast<const __nv_bfloat16*>(a);
   __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
   // the attribute is per device; setting it is cheap, so it is set on every call

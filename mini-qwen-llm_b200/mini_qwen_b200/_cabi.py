@@ -40,6 +40,8 @@ PROTOTYPES = {
     "mq_ep_barrier": (c_int, [_P, _P, _L, _L, _P, _P]),
     "mq_ep_plan": (c_int, [_P, _L, _L, _L, _P, _P, _P, _L, _P, _P]),
     "mq_ep_dispatch": (c_int, [_P, _I, _P, _P, _P, _L, _L, _L, _L, _L, _P, _L, _P, _P, _P]),
+    "mq_ep_unique_rows": (c_int, [_P, _L, _L, _L, _L, _P, _P]),
+    "mq_ep_dispatch_unique": (c_int, [_P, _I, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _P, _P, _L, _P, _P, _P]),
     "mq_ep_combine": (c_int, [_P, _I, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
 }
 

@@ -86,13 +86,15 @@ def moe_grouped_swiglu_gather(hidden_states: torch.Tensor, perm: torch.Tensor, t
                               gate_up_weights: torch.Tensor, expert_offsets: torch.Tensor,
                               status: torch.Tensor | None = None) -> torch.Tensor:
     """:func:`moe_grouped_swiglu` on ``hidden_states[perm // top_k]`` without materialising the
-    permuted rows: the kernel gathers them itself.  ``hidden_states`` is the unpermuted [T, H]."""
+    permuted rows: the kernel gathers them itself.  ``hidden_states`` is the unpermuted [T, H].
+    ``perm`` may be longer than the slots ``expert_offsets`` covers (a slot table sized for the worst
+    case); the result has one row per entry of ``perm``."""
     _cabi.require_cuda(hidden_states, perm, gate_up_weights, expert_offsets)
     E, I2, H = gate_up_weights.shape
     x = hidden_states.contiguous()
     T = x.shape[0]
     S = perm.numel()
-    assert S == T * top_k and x.shape[1] == H
+    assert x.shape[1] == H
     groups = expert_offsets.numel() - 1
     h = torch.empty(S, I2 // 2, dtype=x.dtype, device=x.device)
     if status is None:

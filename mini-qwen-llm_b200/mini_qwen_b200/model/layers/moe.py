@@ -72,6 +72,9 @@ class Qwen3MoEBlock(nn.Module):
         # "fused": the down projection writes its rows into the source ranks' buffers itself;
         # "pull": the combine kernel reads them from the owners (the only way for W4A16 experts)
         self.ep_return = "fused"
+        # "unique": a token row crosses NVLink once per destination rank and the owner's gate/up kernel
+        # gathers through a slot table; "slots": one copy per slot (W4A16 experts, more than 8 ranks)
+        self.ep_dispatch = "unique"
         self._peer = None
         self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
         self.ep_rank = 0 if ep_group is None else torch.distributed.get_rank(ep_group)
@@ -183,7 +186,7 @@ class Qwen3MoEBlock(nn.Module):
                                 renormalize=self.norm_topk_prob, return_int32_ids=True)
         perm, inv, off32, _ = run("permute_plan", moe_permute_plan, ids32, E, want_int64_offsets=False)
         if self.ep_size > 1 and self.ep_mode == "p2p":
-            return self._forward_peer(x2d, st, weights, perm, inv, off32, T, K, E).reshape(shape)
+            return self._forward_peer(x2d, st, weights, ids32, perm, inv, off32, T, K, E).reshape(shape)
         if self.ep_size == 1 and not st["w4"] and gather_swiglu_supported(x2d, st["w13"]):
             # the gate/up kernel fetches the rows through the permutation itself: no permuted copy
             status = self._status_word(x2d.device)
@@ -230,7 +233,7 @@ class Qwen3MoEBlock(nn.Module):
         if self._peer is not None:
             self._peer.check_status()
 
-    def _forward_peer(self, x2d, st, weights, perm, inv, off32, T, K, E):
+    def _forward_peer(self, x2d, st, weights, ids32, perm, inv, off32, T, K, E):
         """Expert-parallel path over peer memory: rows go straight from x into the owners' receive
         buffers and expert outputs are read straight from the owners while combining."""
         run = self._stage
@@ -247,19 +250,34 @@ class Qwen3MoEBlock(nn.Module):
         run("rank_barrier", peer.rank_barrier)
         # bf16 experts on the tcgen05 kernel send their output rows home from the down projection's own
         # epilogue (NVLink stores under the remaining tiles); other layers are read back by the combine
-        fused_return = (not st["w4"]) and scatter_gemm_supported(peer.recv_rows(), st["w2"]) \
-            and self.ep_return == "fused"
+        tc5 = (not st["w4"]) and scatter_gemm_supported(peer.recv_rows(), st["w2"]) \
+            and gather_swiglu_supported(peer.recv_rows(), st["w13"])
+        fused_return = tc5 and self.ep_return == "fused"
+        unique = tc5 and self.ep_dispatch == "unique" and self.ep_size <= 8
         send_base, seg, ret = run("ep_plan", peer.plan, all_counts, fused_return)
-        slot_dst = run("dispatch", peer.dispatch, x2d, perm, off32, send_base, K, E)
+        if unique:
+            # one copy of a token row per destination rank; the owners gather through their slot tables
+            slot_dst = run("dispatch", peer.dispatch_unique, x2d, ids32, perm, off32, send_base, K, E,
+                           self.ep_max_tokens)
+        else:
+            slot_dst = run("dispatch", peer.dispatch, x2d, perm, off32, send_base, K, E)
         run("rank_barrier", peer.rank_barrier)
-        if fused_return:
+        if tc5:
             status = self._status_word(x2d.device)
-            h = run("grouped_swiglu", moe_grouped_swiglu, peer.recv_rows(), st["w13"], seg, zero_init=False,
-                    status=status)
-            run("grouped_down", moe_grouped_gemm_scatter, h, st["w2"], seg, ret, status=status)
+            if unique:
+                h = run("grouped_swiglu", moe_grouped_swiglu_gather, peer.recv_rows(), peer.slot_table(), 1,
+                        st["w13"], seg, status=status)
+            else:
+                h = run("grouped_swiglu", moe_grouped_swiglu, peer.recv_rows(), st["w13"], seg, zero_init=False,
+                        status=status)
+            if fused_return:
+                run("grouped_down", moe_grouped_gemm_scatter, h, st["w2"], seg, ret, status=status)
+                run("rank_barrier", peer.rank_barrier)
+                # every row of this rank's sorted order is back in its own buffer
+                return run("unpermute_combine", unpermute_combine, peer.y_rows()[:T * K], weights, inv, T, K)
+            run("grouped_down", moe_grouped_gemm, h, st["w2"], seg, zero_init=False, out=peer.y_rows(), status=status)
             run("rank_barrier", peer.rank_barrier)
-            # every row of this rank's sorted order is back in its own buffer
-            return run("unpermute_combine", unpermute_combine, peer.y_rows()[:T * K], weights, inv, T, K)
+            return run("combine", peer.combine, weights, inv, slot_dst, T, K)
         self._experts(st, peer.recv_rows(), seg, out=peer.y_rows())
         run("rank_barrier", peer.rank_barrier)
         return run("combine", peer.combine, weights, inv, slot_dst, T, K)

@@ -118,6 +118,7 @@ class PeerExchange:
         self.recv_ptrs = torch.tensor(list(h_recv.buffer_ptrs), dtype=torch.int64, device=device)
         self.y_ptrs = torch.tensor(list(h_y.buffer_ptrs), dtype=torch.int64, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._ridx = None              # symmetric int32 [cap_rows] slot table, created on first use
         self._counts = None            # symmetric [G, E] int32, created on first use (E is not known here)
         self._sig = symm_mem.empty(max(self.world, 32), dtype=torch.int32, device=device)
         self._sig.zero_()
@@ -192,6 +193,40 @@ class PeerExchange:
                                      c.ptr(slot_dst), c.ptr(self.status), c.stream_ptr(x.device))
         c.check(rc, "mq_ep_dispatch")
         c.count_launches(1 if S else 0)
+        return slot_dst
+
+    def slot_table(self) -> torch.Tensor:
+        """int32 [cap_rows], symmetric: for every received slot, the row of the receive buffer that holds
+        its token (written by the sources' ``dispatch_unique``)."""
+        if self._ridx is None:
+            dev = self.status.device
+            self._ridx = self._symm.empty(self.cap_rows, dtype=torch.int32, device=dev)
+            self._ridx.zero_()
+            h = self._symm.rendezvous(self._ridx, self.group)
+            self._handles += (h,)
+            self.ridx_ptrs = torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=dev)
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=self.group)
+        return self._ridx
+
+    def dispatch_unique(self, x: torch.Tensor, topk_ids32, perm, off32, send_base, top_k: int, num_experts: int,
+                        src_stride: int) -> torch.Tensor:
+        """Dispatch that sends a token row once per destination rank; returns slot_dst as ``dispatch`` does.
+        The receivers read their rows through ``slot_table()``."""
+        c = self._cabi
+        T = x.shape[0]
+        self.slot_table()
+        uniq = torch.empty(T, self.world, dtype=torch.int32, device=x.device)
+        rc = c.load().mq_ep_unique_rows(c.ptr(topk_ids32), T, top_k, num_experts, self.world, c.ptr(uniq),
+                                        c.stream_ptr(x.device))
+        c.check(rc, "mq_ep_unique_rows")
+        slot_dst = torch.empty(T * top_k, dtype=torch.int32, device=x.device)
+        rc = c.load().mq_ep_dispatch_unique(c.ptr(x), c.dtype_code(x), c.ptr(uniq), c.ptr(perm), c.ptr(off32),
+                                            c.ptr(send_base), T, top_k, x.shape[1], num_experts, self.world, self.rank,
+                                            src_stride, c.ptr(self.recv_ptrs), c.ptr(self.ridx_ptrs), self.cap_rows,
+                                            c.ptr(slot_dst), c.ptr(self.status), c.stream_ptr(x.device))
+        c.check(rc, "mq_ep_dispatch_unique")
+        c.count_launches(2 if T else 0)
         return slot_dst
 
     def combine(self, weights, inv, slot_dst, num_tokens: int, top_k: int) -> torch.Tensor:

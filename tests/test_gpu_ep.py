@@ -74,11 +74,11 @@ def _worker(rank, world, port, w4, mode):
         assert torch.equal(blk(x), out)                      # deterministic across calls
         if mode == "p2p":
             blk._peer.check_status()                          # no receive-buffer overflow
-            # the down projection delivering its rows itself and the combine fetching them give the same bits
-            blk.ep_return = "pull"
-            assert torch.equal(blk(x), out)
-            blk.ep_return = "fused"
-            assert torch.equal(blk(x), out)
+            # return by the down projection's own stores or by the combine's loads, dispatch per slot or per
+            # (token, rank): all four give the same bits
+            for ret, disp in (("pull", "unique"), ("pull", "slots"), ("fused", "slots"), ("fused", "unique")):
+                blk.ep_return, blk.ep_dispatch = ret, disp
+                assert torch.equal(blk(x), out), (ret, disp)
             blk.check_status()
             from mini_qwen_b200.graph import CapturedForward
             cap = CapturedForward(blk, x)                     # collective: every rank captures and replays
