@@ -135,16 +135,18 @@ int mq_grouped_gemm(const void* a, const void* w, const int32_t* offsets,
                     int64_t S, int64_t E, int64_t weight_period, int64_t N, int64_t Kd, int dtype,
                     void* out, int32_t* d_status, void* stream);
 
-/* mq_grouped_gemm with one destination per group: the rows of group g are written from address
- * group_out[g] on (row r of the group at group_out[g] + (r - offsets[g]) * N elements) instead of
- * into one [S,N] tensor.  The addresses may lie in another GPU's memory (peer-mapped): expert
- * parallelism uses this to send every expert output row back to the rank it came from out of the
- * GEMM's own epilogue, so the transfer overlaps the remaining tiles.  No counterpart in the
- * reference (it is single-GPU).  group_out: device array of E addresses, each 16-byte aligned.
- * bf16, Kd % 64 == 0, N % 128 == 0 only (MQ_ERR_UNSUPPORTED_SHAPE otherwise). */
+/* mq_grouped_gemm with one destination per output ROW instead of one [S,N] tensor: row r is written
+ * to row (row_dst[r] & 0x3FFFFFF) of the [*, N] buffer at dst_bases[row_dst[r] >> 26].  The buffers
+ * may lie in another GPU's memory (peer-mapped): expert parallelism uses this to send every expert
+ * output row back to the rank and position it came from out of the GEMM's own epilogue, so the
+ * transfer overlaps the remaining tiles.  No counterpart in the reference (it is single-GPU).
+ * row_dst int32 [S] (read for rows inside the groups only); dst_bases: device array of buffer
+ * addresses, each 16-byte aligned.  bf16, Kd % 64 == 0, N % 128 == 0 only
+ * (MQ_ERR_UNSUPPORTED_SHAPE otherwise). */
 int mq_grouped_gemm_scatter(const void* a, const void* w, const int32_t* offsets,
-                            const int64_t* group_out, int64_t S, int64_t E, int64_t weight_period,
-                            int64_t N, int64_t Kd, int dtype, int32_t* d_status, void* stream);
+                            const int32_t* row_dst, const uint64_t* dst_bases, int64_t S, int64_t E,
+                            int64_t weight_period, int64_t N, int64_t Kd, int dtype, int32_t* d_status,
+                            void* stream);
 
 /* Fused gate/up projection with SwiGLU. Replaces _ExpertMLP's first half
  * (mini_qwen/model/layers/moe.py:24-25) for all experts at once:
@@ -197,56 +199,62 @@ int mq_w4a16_grouped_swiglu(const void* x,
  * Expert parallelism over peer memory (no counterpart in the reference, which is single-GPU).
  * G ranks, rank r owns experts [r*E/G, (r+1)*E/G).  Every rank provides a receive buffer and an
  * expert-output buffer of cap_rows rows that its peers can address (peer_*_ptrs: device array of
- * G base addresses, entry r being the local buffer).  Rows received by a rank are grouped by
- * (source rank, local expert).  None of these kernels waits on another GPU; the caller orders the
- * ranks between the calls (a stream-ordered collective).
+ * G base addresses, entry r being the local buffer).  The slots a rank receives are ordered by
+ * local expert and, inside an expert, by source rank (each source's slots in its own sorted order):
+ * E/G ordinary groups for the grouped kernels.  None of these kernels waits on another GPU; the
+ * caller orders the ranks between the calls (mq_ep_barrier or any stream-ordered collective).
  *
- * mq_ep_plan: all_counts int32 [G,E] (per-expert slot counts of every rank) ->
- *   send_base int32 [E]: row in the owner's receive buffer where this rank's rows of expert e start;
- *   seg_offsets int32 [E+1]: prefix sums of this rank's G*(E/G) receive groups;
- *   return_base int64 [E] (optional, with peer_y_ptrs and row_bytes; NULL to skip): for receive group
- *   g = (source s, local expert j), the address in rank s's output buffer of the row at which that
- *   group starts in rank s's expert-sorted order.  Passed as group_out to mq_grouped_gemm_scatter,
- *   it makes the down projection deliver every output row to the position it left from, so the
- *   source finishes with a local mq_unpermute_combine instead of mq_ep_combine.
- * mq_ep_dispatch: fused permute + dispatch.  Row p of the expert-sorted order (token perm[p]/K of x)
- *   is written into the owner's receive buffer; slot_dst[p] = owner * cap_rows + row (or -1 and
- *   status bit 2 when the row would not fit in cap_rows).
- * mq_ep_combine: fused combine + unpermute.  out[t,:] = cast(sum_k weights[t,k] *
- *   float(y_owner[slot_dst[inv[t*K+k]]])), fp32 multiply then add, k ascending.
- */
-/* mq_ep_share_counts: writes this rank's per-expert counts (from its offsets [E+1]) into row `rank`
+ * mq_ep_share_counts: writes this rank's per-expert counts (from its offsets [E+1]) into row `rank`
  *   of every peer's counts table int32 [G,E] (peer_counts_ptrs: G base addresses).
  * mq_ep_barrier: stream-ordered barrier across the G ranks through a signal array int32 [G] on every
  *   rank (peer_signal_ptrs) and a local epoch counter.  The wait is bounded (about a second); on
- *   expiry MQ_DEV_WAIT_EXPIRED is set in d_status and the kernel returns. */
+ *   expiry MQ_DEV_WAIT_EXPIRED is set in d_status and the kernel returns.
+ * mq_ep_plan: all_counts int32 [G,E] (per-expert slot counts of every rank) ->
+ *   send_base int32 [E]: slot in the owner's receive order where this rank's slots of expert e start;
+ *   seg_offsets int32 [E/G+1]: prefix sums of this rank's receive groups (one per local expert).
+ * mq_ep_dispatch: fused permute + dispatch, one row per slot.  Row p of the expert-sorted order
+ *   (token perm[p]/K of x) is written into the owner's receive buffer at its slot;
+ *   slot_dst[p] = owner * cap_rows + slot (or -1 and status bit 2 when it would not fit in cap_rows).
+ *   peer_home_ptrs (optional): the owners' home tables int32 [cap_rows]; entry [slot] becomes
+ *   rank << 26 | p, the row_dst code that makes mq_grouped_gemm_scatter (dst_bases = the ranks'
+ *   output buffers) deliver the slot's output row to row p of this rank's buffer, after which the
+ *   source finishes with a local mq_unpermute_combine instead of mq_ep_combine.
+ * mq_ep_combine: fused combine + unpermute.  out[t,:] = cast(sum_k weights[t,k] *
+ *   float(y_owner[slot_dst[inv[t*K+k]]])), fp32 multiply then add, k ascending.
+ */
 int mq_ep_share_counts(const int32_t* offsets, int64_t E, int64_t G, int64_t rank,
                        const uint64_t* peer_counts_ptrs, void* stream);
 int mq_ep_barrier(const uint64_t* peer_signal_ptrs, int32_t* epoch_counter, int64_t G, int64_t rank,
                   int32_t* d_status, void* stream);
 int mq_ep_plan(const int32_t* all_counts, int64_t G, int64_t rank, int64_t E,
-               int32_t* send_base, int32_t* seg_offsets,
-               const uint64_t* peer_y_ptrs, int64_t row_bytes, int64_t* return_base, void* stream);
+               int32_t* send_base, int32_t* seg_offsets, void* stream);
+/* mq_ep_share_counts, mq_ep_barrier and mq_ep_plan in one launch (the plan is formed from this rank's
+ * own counts table, peer_counts_ptrs[rank], once every rank has written its row). */
+int mq_ep_exchange_plan(const int32_t* offsets, int64_t E, int64_t G, int64_t rank,
+                        const uint64_t* peer_counts_ptrs, const uint64_t* peer_signal_ptrs,
+                        int32_t* epoch_counter, int32_t* send_base, int32_t* seg_offsets,
+                        int32_t* d_status, void* stream);
 int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, const int32_t* offsets,
                    const int32_t* send_base, int64_t S, int64_t K, int64_t H, int64_t E, int64_t G,
-                   const uint64_t* peer_recv_ptrs, int64_t cap_rows, int32_t* slot_dst,
-                   int32_t* d_status, void* stream);
+                   int64_t rank, const uint64_t* peer_recv_ptrs, const uint64_t* peer_home_ptrs,
+                   int64_t cap_rows, int32_t* slot_dst, int32_t* d_status, void* stream);
 /* Dispatch that sends a token row once per destination RANK instead of once per slot (a token with
  * several experts on one GPU crosses NVLink once).  G <= 8.
  * mq_ep_unique_rows: topk_ids int32 [T,K] -> uniq int32 [T,G]: index of token t among this rank's
  *   tokens that have an expert on rank d, in token order, or -1 when it has none there.
  * mq_ep_dispatch_unique: row t goes to row rank*src_stride + uniq[t,d] of every rank d that needs it
- *   (T <= src_stride, G*src_stride <= cap_rows), and every slot's row number goes to its place in the
- *   owner's slot table peer_ridx_ptrs[d] (int32 [cap_rows], (source, local expert) order, the order
- *   seg_offsets describes).  The owner runs mq_grouped_swiglu_gather with x = its receive buffer,
- *   perm = its slot table, top_k = 1.  slot_dst as in mq_ep_dispatch. */
+ *   (T <= src_stride, G*src_stride <= cap_rows), and every slot's row number goes to its slot in the
+ *   owner's slot table peer_ridx_ptrs[d] (int32 [cap_rows]).  The owner runs
+ *   mq_grouped_swiglu_gather with x = its receive buffer, perm = its slot table, top_k = 1.
+ *   slot_dst and peer_home_ptrs as in mq_ep_dispatch. */
 int mq_ep_unique_rows(const int32_t* topk_ids, int64_t T, int64_t K, int64_t E, int64_t G,
                       int32_t* uniq, void* stream);
 int mq_ep_dispatch_unique(const void* x, int dtype, const int32_t* uniq, const int32_t* perm,
                           const int32_t* offsets, const int32_t* send_base, int64_t T, int64_t K,
                           int64_t H, int64_t E, int64_t G, int64_t rank, int64_t src_stride,
                           const uint64_t* peer_recv_ptrs, const uint64_t* peer_ridx_ptrs,
-                          int64_t cap_rows, int32_t* slot_dst, int32_t* d_status, void* stream);
+                          const uint64_t* peer_home_ptrs, int64_t cap_rows, int32_t* slot_dst,
+                          int32_t* d_status, void* stream);
 int mq_ep_combine(const uint64_t* peer_y_ptrs, int dtype, const float* weights, const int32_t* inv,
                   const int32_t* slot_dst, int64_t T, int64_t K, int64_t H, int64_t cap_rows,
                   void* out, void* stream);

@@ -13,7 +13,7 @@ int grouped_gemm_generic_dispatch(const void* a, const void* w, const int32_t* o
 // tcgen05 kernel (bf16). Returns MQ_ERR_UNSUPPORTED_SHAPE when the shape is outside its cover.
 int grouped_gemm_tc5(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E, int64_t period,
                      int64_t N, int64_t Kd, bool swiglu, void* out, int32_t* d_status, cudaStream_t st,
-                     const int32_t* perm, int64_t top_k, const int64_t* group_out);
+                     const int32_t* perm, int64_t top_k, const int32_t* row_dst, const uint64_t* dst_bases);
 bool tc5_covers(int64_t S, int64_t E, int64_t N, int64_t Kd, bool swiglu);
 
 }  // namespace mq
@@ -48,7 +48,7 @@ static int grouped_common(const void* a, const void* w, const int32_t* offsets, 
   if (!a || !w || !offsets || !out) return MQ_ERR_INVALID_ARGUMENT;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == MQ_BF16 && tc5_covers(S, period, N, Kd, swiglu) && aligned16(a) && aligned16(w) && aligned16(out))
-    return grouped_gemm_tc5(a, w, offsets, S, E, period, N, Kd, swiglu, out, d_status, st, nullptr, 1, nullptr);
+    return grouped_gemm_tc5(a, w, offsets, S, E, period, N, Kd, swiglu, out, d_status, st, nullptr, 1, nullptr, nullptr);
   return grouped_gemm_generic_dispatch(a, w, offsets, S, E, period, N, Kd, dtype, swiglu, out, st);
 }
 
@@ -79,18 +79,19 @@ extern "C" int mq_grouped_swiglu_gather(const void* x, const int32_t* perm, cons
   if (!x || !perm || !w_gate_up || !offsets || !h) return MQ_ERR_INVALID_ARGUMENT;
   if (!aligned16(x) || !aligned16(w_gate_up) || !aligned16(h)) return MQ_ERR_INVALID_ARGUMENT;
   return grouped_gemm_tc5(x, w_gate_up, offsets, S, E, weight_period, I, H, true, h, d_status,
-                          reinterpret_cast<cudaStream_t>(stream), perm, top_k, nullptr);
+                          reinterpret_cast<cudaStream_t>(stream), perm, top_k, nullptr, nullptr);
 }
 
 extern "C" int mq_grouped_gemm_scatter(const void* a, const void* w, const int32_t* offsets,
-                                       const int64_t* group_out, int64_t S, int64_t E, int64_t weight_period,
-                                       int64_t N, int64_t Kd, int dtype, int32_t* d_status, void* stream) {
+                                       const int32_t* row_dst, const uint64_t* dst_bases, int64_t S, int64_t E,
+                                       int64_t weight_period, int64_t N, int64_t Kd, int dtype, int32_t* d_status,
+                                       void* stream) {
   using namespace mq;
   if (S < 0 || E <= 0 || N <= 0 || Kd <= 0 || weight_period <= 0 || weight_period > E || !valid_dtype(dtype))
     return MQ_ERR_INVALID_ARGUMENT;
   if (dtype != MQ_BF16 || !tc5_covers(S, weight_period, N, Kd, false)) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (S == 0) return MQ_OK;
-  if (!a || !w || !offsets || !group_out || !aligned16(a) || !aligned16(w)) return MQ_ERR_INVALID_ARGUMENT;
+  if (!a || !w || !offsets || !row_dst || !dst_bases || !aligned16(a) || !aligned16(w)) return MQ_ERR_INVALID_ARGUMENT;
   return grouped_gemm_tc5(a, w, offsets, S, E, weight_period, N, Kd, false, nullptr, d_status,
-                          reinterpret_cast<cudaStream_t>(stream), nullptr, 1, group_out);
+                          reinterpret_cast<cudaStream_t>(stream), nullptr, 1, row_dst, dst_bases);
 }

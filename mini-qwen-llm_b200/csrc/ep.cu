@@ -8,51 +8,43 @@
 // while forming the weighted sum.  No kernel here waits on another GPU: ordering between the ranks
 // is a stream-ordered collective issued by the host side between the kernels.
 //
-// Receive layout on every rank: rows grouped by (source rank, local expert), i.e. G * E_local groups,
-// which is the group order the grouped GEMM kernels take as it is.
+// Receive layout on every rank: slots grouped by local expert and, inside an expert, by source rank
+// (each source's slots in its own expert-sorted order).  The grouped GEMM kernels see E_local ordinary
+// groups, each expert's weights are streamed once, and rows bound for different ranks alternate
+// inside every tile, which spreads the NVLink traffic of the way back over the whole kernel.
 #include "common.cuh"
 
 namespace mq {
 namespace {
 
+constexpr int EP_MAX_G = 8;
+constexpr int HOME_BITS = 26;        // home code of a slot: source rank << 26 | position in the source's sorted order
+
 // From the gathered per-expert counts [G, E]:
-//   send_base[e]  = row in the owner's receive buffer where this rank's rows for expert e start
-//   seg_offsets[] = prefix sums of this rank's own receive groups, (source, local expert) order
+//   send_base[e]  = slot in the owner's receive order where this rank's slots for expert e start
+//   seg_offsets[] = prefix sums of this rank's own E/G receive groups (one per local expert)
 __global__ void __launch_bounds__(256)
 ep_plan_kernel(const int32_t* __restrict__ all_counts, int G, int rank, int E,
-               int32_t* __restrict__ send_base, int32_t* __restrict__ seg_offsets,
-               const uint64_t* __restrict__ peer_y, int64_t row_bytes, int64_t* __restrict__ return_base) {
+               int32_t* __restrict__ send_base, int32_t* __restrict__ seg_offsets) {
   const int el = E / G;
-  // way back: the rows of receive group (s, j) are rows [P, P + count) of rank s's expert-sorted order,
-  // P = number of rank s's slots on experts before rank * el + j; their outputs go to that place in
-  // rank s's buffer
-  if (return_base != nullptr) {
-    for (int g = threadIdx.x; g < E; g += blockDim.x) {
-      const int s = g / el, j = g - s * el;
-      int64_t before = 0;
-      for (int e = 0; e < rank * el + j; ++e) before += all_counts[s * E + e];
-      return_base[g] = (int64_t)peer_y[s] + before * row_bytes;
-    }
-  }
-  // destination-side bases: one thread per expert, serial prefix over the (source, local expert) groups
-  // that precede (rank, e % el) on the owner of e.  G * el <= 1024 groups: a few hundred adds.
+  // one thread per expert: slots of the owner's earlier experts (all sources), then earlier sources'
+  // slots of this expert.  At most E additions each.
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     const int d = e / el, j = e - d * el;
     int base = 0;
-    for (int s = 0; s < rank; ++s)
-      for (int jj = 0; jj < el; ++jj) base += all_counts[s * E + d * el + jj];
-    for (int jj = 0; jj < j; ++jj) base += all_counts[rank * E + d * el + jj];
+    for (int jj = 0; jj < j; ++jj)
+      for (int s = 0; s < G; ++s) base += all_counts[s * E + d * el + jj];
+    for (int s = 0; s < rank; ++s) base += all_counts[s * E + e];
     send_base[e] = base;
   }
   // own receive groups
   if (threadIdx.x == 0) {
     int run = 0;
-    for (int s = 0; s < G; ++s)
-      for (int j = 0; j < el; ++j) {
-        seg_offsets[s * el + j] = run;
-        run += all_counts[s * E + rank * el + j];
-      }
-    seg_offsets[G * el] = run;
+    for (int j = 0; j < el; ++j) {
+      seg_offsets[j] = run;
+      for (int s = 0; s < G; ++s) run += all_counts[s * E + rank * el + j];
+    }
+    seg_offsets[el] = run;
   }
 }
 
@@ -99,11 +91,72 @@ ep_barrier_kernel(const uint64_t* __restrict__ peer_sig, int32_t* __restrict__ e
   }
 }
 
+// The three steps that open a layer call in one launch: this rank's counts go into every peer's table,
+// the ranks meet (same bounded barrier as above), and the plan is formed from the now complete table.
+__global__ void __launch_bounds__(256)
+ep_exchange_plan_kernel(const int32_t* __restrict__ offsets, int E, int G, int rank,
+                        const uint64_t* __restrict__ peer_counts, const uint64_t* __restrict__ peer_sig,
+                        int32_t* __restrict__ epoch_ctr, int32_t* __restrict__ send_base,
+                        int32_t* __restrict__ seg_offsets, int32_t* __restrict__ status) {
+  __shared__ int s_epoch;
+  __shared__ int s_tot[1024];                    // slots per expert over all sources
+  const int el = E / G;
+  for (int i = threadIdx.x; i < E * G; i += blockDim.x) {
+    const int d = i / E, e = i - d * E;
+    reinterpret_cast<int32_t*>(peer_counts[d])[rank * E + e] = offsets[e + 1] - offsets[e];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    if (threadIdx.x == 0) {
+      s_epoch = *epoch_ctr + 1;
+      *epoch_ctr = s_epoch;
+    }
+    __syncwarp();
+    const int epoch = s_epoch;
+    __threadfence_system();
+    for (int r = threadIdx.x; r < G; r += 32) {
+      int32_t* remote = reinterpret_cast<int32_t*>(peer_sig[r]) + rank;
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    }
+    const int32_t* mine = reinterpret_cast<const int32_t*>(peer_sig[rank]);
+    for (int r = threadIdx.x; r < G; r += 32) {
+      uint32_t spin = 0;
+      int v;
+      do {
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine + r) : "memory");
+      } while (v < epoch && ++spin < EP_SPIN_LIMIT);
+      if (v < epoch) atomicOr(status, (int)MQ_DEV_WAIT_EXPIRED);
+    }
+  }
+  __syncthreads();
+  const int32_t* all_counts = reinterpret_cast<const int32_t*>(peer_counts[rank]);   // [G, E], written by the peers
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0;
+    for (int s = 0; s < G; ++s) tot += __ldcg(all_counts + s * E + e);
+    s_tot[e] = tot;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int d = e / el;
+    int base = 0;
+    for (int ee = d * el; ee < e; ++ee) base += s_tot[ee];
+    for (int s = 0; s < rank; ++s) base += __ldcg(all_counts + s * E + e);
+    send_base[e] = base;
+  }
+  for (int j = threadIdx.x; j <= el; j += blockDim.x) {
+    int run = 0;
+    for (int jj = 0; jj < j; ++jj) run += s_tot[rank * el + jj];
+    seg_offsets[j] = run;
+  }
+}
+
 // One warp per expert-sorted slot p: copy the token row to the owner's receive buffer.
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm,
                    const int32_t* __restrict__ offsets, const int32_t* __restrict__ send_base,
                    int64_t S, int K, int vec_per_row, int E, int el, const uint64_t* __restrict__ peer_recv,
+                   const uint64_t* __restrict__ peer_home, int rank,
                    int64_t cap_rows, int32_t* __restrict__ slot_dst, int32_t* __restrict__ status) {
   const int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (p >= S) return;
@@ -121,7 +174,11 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm
     if (lane == 0) { atomicOr(status, 2); slot_dst[p] = -1; }
     return;
   }
-  if (lane == 0) slot_dst[p] = (int32_t)(d * cap_rows + row);
+  if (lane == 0) {
+    slot_dst[p] = (int32_t)(d * cap_rows + row);
+    // where the slot's output row goes home to: (this rank, sorted position p)
+    if (peer_home != nullptr) reinterpret_cast<int32_t*>(peer_home[d])[row] = (rank << HOME_BITS) | (int32_t)p;
+  }
   const uint4* src = x + (int64_t)(perm[p] / K) * vec_per_row;
   uint4* dst = reinterpret_cast<uint4*>(peer_recv[d]) + row * vec_per_row;
   for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(src + v);
@@ -133,7 +190,7 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm
 // -1; the row travels to row rank * src_stride + uniq[t, d] of rank d's receive buffer, and every
 // slot carries only that row number (4 bytes) to its place in the (source, local expert) order.  The
 // gate/up kernel of the owner then gathers its rows through those numbers.
-constexpr int EP_MAX_G = 8;
+
 
 __global__ void __launch_bounds__(1024)
 ep_unique_rows_kernel(const int32_t* __restrict__ ids, int T, int K, int el, int G, int32_t* __restrict__ uniq) {
@@ -186,6 +243,7 @@ ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict
                           const int32_t* __restrict__ send_base, int T, int64_t S, int K, int vec_per_row, int E,
                           int el, int G, int rank, int src_stride, int row_blocks,
                           const uint64_t* __restrict__ peer_recv, const uint64_t* __restrict__ peer_ridx,
+                          const uint64_t* __restrict__ peer_home,
                           int64_t cap_rows, int32_t* __restrict__ slot_dst, int32_t* __restrict__ status) {
   if ((int)blockIdx.x < row_blocks) {
     const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -224,6 +282,7 @@ ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict
   }
   slot_dst[p] = (int32_t)(d * cap_rows + row);
   reinterpret_cast<int32_t*>(peer_ridx[d])[row] = rank * src_stride + uniq[(int64_t)(perm[p] / K) * G + d];
+  if (peer_home != nullptr) reinterpret_cast<int32_t*>(peer_home[d])[row] = (rank << HOME_BITS) | (int32_t)p;
 }
 
 // out[t,:] = cast(sum_k w[t,k] * float(y_on_owner[slot row, :])), fp32 multiply then add, k ascending.
@@ -289,16 +348,13 @@ int launch_ep_combine(const uint64_t* peer_y, const float* weights, const int32_
 }  // namespace mq
 
 extern "C" int mq_ep_plan(const int32_t* all_counts, int64_t G, int64_t rank, int64_t E,
-                          int32_t* send_base, int32_t* seg_offsets,
-                          const uint64_t* peer_y_ptrs, int64_t row_bytes, int64_t* return_base, void* stream) {
+                          int32_t* send_base, int32_t* seg_offsets, void* stream) {
   using namespace mq;
   if (G <= 0 || E <= 0 || rank < 0 || rank >= G || E % G != 0) return MQ_ERR_INVALID_ARGUMENT;
   if (E > 1024) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (!all_counts || !send_base || !seg_offsets) return MQ_ERR_INVALID_ARGUMENT;
-  if (return_base != nullptr && (!peer_y_ptrs || row_bytes <= 0 || row_bytes % 16 != 0)) return MQ_ERR_INVALID_ARGUMENT;
   ep_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(all_counts, (int)G, (int)rank, (int)E,
-                                                                       send_base, seg_offsets, peer_y_ptrs,
-                                                                       row_bytes, return_base);
+                                                                       send_base, seg_offsets);
   return check_launch();
 }
 
@@ -322,11 +378,13 @@ extern "C" int mq_ep_barrier(const uint64_t* peer_signal_ptrs, int32_t* epoch_co
 
 extern "C" int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, const int32_t* offsets,
                               const int32_t* send_base, int64_t S, int64_t K, int64_t H, int64_t E, int64_t G,
-                              const uint64_t* peer_recv_ptrs, int64_t cap_rows, int32_t* slot_dst,
-                              int32_t* d_status, void* stream) {
+                              int64_t rank, const uint64_t* peer_recv_ptrs, const uint64_t* peer_home_ptrs,
+                              int64_t cap_rows, int32_t* slot_dst, int32_t* d_status, void* stream) {
   using namespace mq;
   if (S < 0 || K <= 0 || H <= 0 || E <= 0 || G <= 0 || E % G != 0 || !valid_dtype(dtype)) return MQ_ERR_INVALID_ARGUMENT;
+  if (rank < 0 || rank >= G) return MQ_ERR_INVALID_ARGUMENT;
   if (cap_rows <= 0 || G * cap_rows >= ((int64_t)1 << 31)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (peer_home_ptrs && (S > ((int64_t)1 << HOME_BITS) || G > 32)) return MQ_ERR_UNSUPPORTED_SHAPE;
   const int64_t row_bytes = H * (int64_t)dtype_size(dtype);
   if (row_bytes % 16 != 0) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (S == 0) return MQ_OK;
@@ -334,7 +392,7 @@ extern "C" int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, con
   if (!aligned16(x)) return MQ_ERR_INVALID_ARGUMENT;
   ep_dispatch_kernel<<<(unsigned)((S + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(x), perm, offsets, send_base, S, (int)K, (int)(row_bytes / 16), (int)E,
-      (int)(E / G), peer_recv_ptrs, cap_rows, slot_dst, d_status);
+      (int)(E / G), peer_recv_ptrs, peer_home_ptrs, (int)rank, cap_rows, slot_dst, d_status);
   return check_launch();
 }
 
@@ -368,11 +426,12 @@ extern "C" int mq_ep_dispatch_unique(const void* x, int dtype, const int32_t* un
                                      const int32_t* offsets, const int32_t* send_base, int64_t T, int64_t K,
                                      int64_t H, int64_t E, int64_t G, int64_t rank, int64_t src_stride,
                                      const uint64_t* peer_recv_ptrs, const uint64_t* peer_ridx_ptrs,
-                                     int64_t cap_rows, int32_t* slot_dst, int32_t* d_status, void* stream) {
+                                     const uint64_t* peer_home_ptrs, int64_t cap_rows, int32_t* slot_dst,
+                                     int32_t* d_status, void* stream) {
   using namespace mq;
   if (T < 0 || K <= 0 || H <= 0 || E <= 0 || G <= 0 || E % G != 0 || rank < 0 || rank >= G || !valid_dtype(dtype))
     return MQ_ERR_INVALID_ARGUMENT;
-  if (G > EP_MAX_G || cap_rows <= 0 || G * cap_rows >= ((int64_t)1 << 31) || T * K >= ((int64_t)1 << 31))
+  if (G > EP_MAX_G || cap_rows <= 0 || G * cap_rows >= ((int64_t)1 << 31) || T * K > ((int64_t)1 << HOME_BITS))
     return MQ_ERR_UNSUPPORTED_SHAPE;
   // every source owns src_stride rows of every receive buffer
   if (T > src_stride || G * src_stride > cap_rows) return MQ_ERR_INVALID_ARGUMENT;
@@ -388,6 +447,21 @@ extern "C" int mq_ep_dispatch_unique(const void* x, int dtype, const int32_t* un
   ep_dispatch_unique_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(x), uniq, perm, offsets, send_base, (int)T, S, (int)K, (int)(row_bytes / 16),
       (int)E, (int)(E / G), (int)G, (int)rank, (int)src_stride, row_blocks, peer_recv_ptrs, peer_ridx_ptrs,
-      cap_rows, slot_dst, d_status);
+      peer_home_ptrs, cap_rows, slot_dst, d_status);
+  return check_launch();
+}
+
+extern "C" int mq_ep_exchange_plan(const int32_t* offsets, int64_t E, int64_t G, int64_t rank,
+                                   const uint64_t* peer_counts_ptrs, const uint64_t* peer_signal_ptrs,
+                                   int32_t* epoch_counter, int32_t* send_base, int32_t* seg_offsets,
+                                   int32_t* d_status, void* stream) {
+  using namespace mq;
+  if (E <= 0 || G <= 0 || rank < 0 || rank >= G || E % G != 0) return MQ_ERR_INVALID_ARGUMENT;
+  if (E > 1024) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (!offsets || !peer_counts_ptrs || !peer_signal_ptrs || !epoch_counter || !send_base || !seg_offsets || !d_status)
+    return MQ_ERR_INVALID_ARGUMENT;
+  ep_exchange_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      offsets, (int)E, (int)G, (int)rank, peer_counts_ptrs, peer_signal_ptrs, epoch_counter, send_base, seg_offsets,
+      d_status);
   return check_launch();
 }

@@ -116,20 +116,24 @@ def scatter_gemm_supported(rows: torch.Tensor, expert_weights: torch.Tensor) -> 
 
 
 def moe_grouped_gemm_scatter(rows: torch.Tensor, expert_weights: torch.Tensor, expert_offsets: torch.Tensor,
-                             group_out: torch.Tensor, status: torch.Tensor | None = None) -> None:
-    """:func:`moe_grouped_gemm` whose output rows go to one destination per group: group g's rows are
-    written from address ``group_out[g]`` (int64 device addresses, possibly in a peer GPU's memory) on.
-    Nothing is returned; the caller owns the destination buffers and the ordering with their readers."""
-    _cabi.require_cuda(rows, expert_weights, expert_offsets, group_out)
+                             row_dst: torch.Tensor, dst_bases: torch.Tensor,
+                             status: torch.Tensor | None = None) -> None:
+    """:func:`moe_grouped_gemm` whose output rows go to one destination each: row r is written to row
+    ``row_dst[r] & 0x3FFFFFF`` of the ``[*, N]`` buffer at address ``dst_bases[row_dst[r] >> 26]`` (int64
+    device addresses, possibly in a peer GPU's memory).  Nothing is returned; the caller owns the
+    destination buffers and the ordering with their readers."""
+    _cabi.require_cuda(rows, expert_weights, expert_offsets, row_dst, dst_bases)
     E, N, Kd = expert_weights.shape
     a = rows.contiguous()
     S = a.shape[0]
     groups = expert_offsets.numel() - 1
-    assert group_out.dtype == torch.int64 and group_out.numel() == groups and a.shape[1] == Kd
+    assert row_dst.dtype == torch.int32 and row_dst.numel() >= S and dst_bases.dtype == torch.int64
+    assert a.shape[1] == Kd
     if status is None:
         status = _status_word(a.device)
     rc = _cabi.load().mq_grouped_gemm_scatter(_cabi.ptr(a), _cabi.ptr(expert_weights),
-                                              _cabi.ptr(_offsets32(expert_offsets)), _cabi.ptr(group_out), S, groups, E,
-                                              N, Kd, _cabi.dtype_code(a), _cabi.ptr(status), _cabi.stream_ptr(a.device))
+                                              _cabi.ptr(_offsets32(expert_offsets)), _cabi.ptr(row_dst),
+                                              _cabi.ptr(dst_bases), S, groups, E, N, Kd, _cabi.dtype_code(a),
+                                              _cabi.ptr(status), _cabi.stream_ptr(a.device))
     _cabi.check(rc, "mq_grouped_gemm_scatter")
     _cabi.count_launches(1 if S else 0)

@@ -246,15 +246,12 @@ class Qwen3MoEBlock(nn.Module):
         if T > self.ep_max_tokens or x2d.dtype != peer.dtype:
             raise ValueError(f"expert-parallel buffers were sized for {self.ep_max_tokens} tokens of {peer.dtype} per "
                              f"rank; got {T} of {x2d.dtype} (pass ep_max_tokens at construction)")
-        all_counts = run("share_counts", peer.share_counts, off32)
-        run("rank_barrier", peer.rank_barrier)
-        # bf16 experts on the tcgen05 kernel send their output rows home from the down projection's own
-        # epilogue (NVLink stores under the remaining tiles); other layers are read back by the combine
         tc5 = (not st["w4"]) and scatter_gemm_supported(peer.recv_rows(), st["w2"]) \
             and gather_swiglu_supported(peer.recv_rows(), st["w13"])
         fused_return = tc5 and self.ep_return == "fused"
         unique = tc5 and self.ep_dispatch == "unique" and self.ep_size <= 8
-        send_base, seg, ret = run("ep_plan", peer.plan, all_counts, fused_return)
+        # counts to every peer, rank barrier, plan: one launch
+        send_base, seg = run("exchange_plan", peer.exchange_plan, off32)
         if unique:
             # one copy of a token row per destination rank; the owners gather through their slot tables
             slot_dst = run("dispatch", peer.dispatch_unique, x2d, ids32, perm, off32, send_base, K, E,
@@ -271,7 +268,8 @@ class Qwen3MoEBlock(nn.Module):
                 h = run("grouped_swiglu", moe_grouped_swiglu, peer.recv_rows(), st["w13"], seg, zero_init=False,
                         status=status)
             if fused_return:
-                run("grouped_down", moe_grouped_gemm_scatter, h, st["w2"], seg, ret, status=status)
+                run("grouped_down", moe_grouped_gemm_scatter, h, st["w2"], seg, peer.home_table(), peer.y_ptrs,
+                    status=status)
                 run("rank_barrier", peer.rank_barrier)
                 # every row of this rank's sorted order is back in its own buffer
                 return run("unpermute_combine", unpermute_combine, peer.y_rows()[:T * K], weights, inv, T, K)

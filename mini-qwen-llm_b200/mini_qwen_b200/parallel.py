@@ -93,6 +93,8 @@ class PeerExchange:
     addresses; the data path is this library's kernels).  ``cap_rows`` defaults to the worst case,
     every slot of every rank landing on one GPU, so no routing can overflow it.
 
+    Received slots are ordered by local expert and, inside an expert, by source rank.
+
     Ordering between ranks is three stream-ordered barriers per layer call: after the counts have
     been shared, after the dispatch kernels and after the down projection.  The barrier is a
     one-warp kernel that writes an epoch into every peer's signal array and polls its own, with a
@@ -118,7 +120,7 @@ class PeerExchange:
         self.recv_ptrs = torch.tensor(list(h_recv.buffer_ptrs), dtype=torch.int64, device=device)
         self.y_ptrs = torch.tensor(list(h_y.buffer_ptrs), dtype=torch.int64, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self._ridx = None              # symmetric int32 [cap_rows] slot table, created on first use
+        self._tab = None               # symmetric int32 [2, cap_rows]: slot table and home table
         self._counts = None            # symmetric [G, E] int32, created on first use (E is not known here)
         self._sig = symm_mem.empty(max(self.world, 32), dtype=torch.int32, device=device)
         self._sig.zero_()
@@ -151,11 +153,7 @@ class PeerExchange:
         after the next rank_barrier()."""
         E = off32.numel() - 1
         dev = off32.device
-        if self._counts is None or self._counts.numel() != self.world * E:
-            self._counts = self._symm.empty(self.world * E, dtype=torch.int32, device=dev)
-            h = self._symm.rendezvous(self._counts, self.group)
-            self._handles += (h,)
-            self.counts_ptrs = torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=dev)
+        self._counts_table(E, dev)
         c = self._cabi
         rc = c.load().mq_ep_share_counts(c.ptr(off32), E, self.world, self.rank, c.ptr(self.counts_ptrs),
                                          c.stream_ptr(dev))
@@ -163,51 +161,78 @@ class PeerExchange:
         c.count_launches(1)
         return self._counts.view(self.world, E)
 
-    def plan(self, all_counts: torch.Tensor, with_return: bool = False):
-        """Device-side plan (no host sync): (send_base int32 [E], seg_offsets int32 [E+1], return_base).
+    def _counts_table(self, E: int, dev) -> None:
+        if self._counts is None or self._counts.numel() != self.world * E:
+            self._counts = self._symm.empty(self.world * E, dtype=torch.int32, device=dev)
+            h = self._symm.rendezvous(self._counts, self.group)
+            self._handles += (h,)
+            self.counts_ptrs = torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=dev)
 
-        ``return_base`` (int64 [E], only ``with_return``) holds, for every receive group (source, local
-        expert), the address in the SOURCE's output buffer where that group's rows sit in the source's
-        expert-sorted order: the down projection writes its output rows there itself."""
+    def exchange_plan(self, off32: torch.Tensor):
+        """``share_counts``, ``rank_barrier`` and ``plan`` in one launch: (send_base, seg_offsets)."""
+        E = off32.numel() - 1
+        dev = off32.device
+        self._counts_table(E, dev)
+        send_base = torch.empty(E, dtype=torch.int32, device=dev)
+        seg = torch.empty(E // self.world + 1, dtype=torch.int32, device=dev)
+        c = self._cabi
+        rc = c.load().mq_ep_exchange_plan(c.ptr(off32), E, self.world, self.rank, c.ptr(self.counts_ptrs),
+                                          c.ptr(self.sig_ptrs), c.ptr(self._epoch), c.ptr(send_base), c.ptr(seg),
+                                          c.ptr(self.status), c.stream_ptr(dev))
+        c.check(rc, "mq_ep_exchange_plan")
+        c.count_launches(1)
+        return send_base, seg
+
+    def plan(self, all_counts: torch.Tensor):
+        """Device-side plan (no host sync): (send_base int32 [E], seg_offsets int32 [E/G + 1])."""
         G, E = all_counts.shape
         dev = all_counts.device
         send_base = torch.empty(E, dtype=torch.int32, device=dev)
-        seg = torch.empty(E + 1, dtype=torch.int32, device=dev)
-        ret = torch.empty(E, dtype=torch.int64, device=dev) if with_return else None
+        seg = torch.empty(E // G + 1, dtype=torch.int32, device=dev)
         c = self._cabi
-        row_bytes = self.hidden * self.y.element_size()
-        rc = c.load().mq_ep_plan(c.ptr(all_counts), G, self.rank, E, c.ptr(send_base), c.ptr(seg),
-                                 c.ptr(self.y_ptrs) if with_return else None, row_bytes,
-                                 c.ptr(ret) if with_return else None, c.stream_ptr(dev))
+        rc = c.load().mq_ep_plan(c.ptr(all_counts), G, self.rank, E, c.ptr(send_base), c.ptr(seg), c.stream_ptr(dev))
         c.check(rc, "mq_ep_plan")
         c.count_launches(1)
-        return send_base, seg, ret
+        return send_base, seg
 
     def dispatch(self, x: torch.Tensor, perm, off32, send_base, top_k: int, num_experts: int) -> torch.Tensor:
-        """Fused permute + dispatch; returns slot_dst int32 [S] (owner * cap_rows + row)."""
+        """Fused permute + dispatch, one row per slot; returns slot_dst int32 [S] (owner * cap_rows + slot).
+        Also fills the owners' home tables (where each slot's output row goes back to)."""
         c = self._cabi
         S = perm.numel()
+        self._tables()
         slot_dst = torch.empty(S, dtype=torch.int32, device=x.device)
         rc = c.load().mq_ep_dispatch(c.ptr(x), c.dtype_code(x), c.ptr(perm), c.ptr(off32), c.ptr(send_base), S, top_k,
-                                     x.shape[1], num_experts, self.world, c.ptr(self.recv_ptrs), self.cap_rows,
-                                     c.ptr(slot_dst), c.ptr(self.status), c.stream_ptr(x.device))
+                                     x.shape[1], num_experts, self.world, self.rank, c.ptr(self.recv_ptrs),
+                                     c.ptr(self.home_ptrs), self.cap_rows, c.ptr(slot_dst), c.ptr(self.status),
+                                     c.stream_ptr(x.device))
         c.check(rc, "mq_ep_dispatch")
         c.count_launches(1 if S else 0)
         return slot_dst
 
-    def slot_table(self) -> torch.Tensor:
-        """int32 [cap_rows], symmetric: for every received slot, the row of the receive buffer that holds
-        its token (written by the sources' ``dispatch_unique``)."""
-        if self._ridx is None:
+    def _tables(self) -> None:
+        """Symmetric int32 [2, cap_rows], created on first use: row 0 the slot table (for every received
+        slot, the row of the receive buffer that holds its token; written by ``dispatch_unique``), row 1
+        the home table (source rank << 26 | position in the source's sorted order)."""
+        if self._tab is None:
             dev = self.status.device
-            self._ridx = self._symm.empty(self.cap_rows, dtype=torch.int32, device=dev)
-            self._ridx.zero_()
-            h = self._symm.rendezvous(self._ridx, self.group)
+            self._tab = self._symm.empty(2 * self.cap_rows, dtype=torch.int32, device=dev)
+            self._tab.zero_()
+            h = self._symm.rendezvous(self._tab, self.group)
             self._handles += (h,)
-            self.ridx_ptrs = torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=dev)
+            ptrs = list(h.buffer_ptrs)
+            self.ridx_ptrs = torch.tensor(ptrs, dtype=torch.int64, device=dev)
+            self.home_ptrs = torch.tensor([q + 4 * self.cap_rows for q in ptrs], dtype=torch.int64, device=dev)
             torch.cuda.synchronize(dev)
             dist.barrier(group=self.group)
-        return self._ridx
+
+    def slot_table(self) -> torch.Tensor:
+        self._tables()
+        return self._tab[:self.cap_rows]
+
+    def home_table(self) -> torch.Tensor:
+        self._tables()
+        return self._tab[self.cap_rows:]
 
     def dispatch_unique(self, x: torch.Tensor, topk_ids32, perm, off32, send_base, top_k: int, num_experts: int,
                         src_stride: int) -> torch.Tensor:
@@ -215,7 +240,7 @@ class PeerExchange:
         The receivers read their rows through ``slot_table()``."""
         c = self._cabi
         T = x.shape[0]
-        self.slot_table()
+        self._tables()
         uniq = torch.empty(T, self.world, dtype=torch.int32, device=x.device)
         rc = c.load().mq_ep_unique_rows(c.ptr(topk_ids32), T, top_k, num_experts, self.world, c.ptr(uniq),
                                         c.stream_ptr(x.device))
@@ -223,8 +248,8 @@ class PeerExchange:
         slot_dst = torch.empty(T * top_k, dtype=torch.int32, device=x.device)
         rc = c.load().mq_ep_dispatch_unique(c.ptr(x), c.dtype_code(x), c.ptr(uniq), c.ptr(perm), c.ptr(off32),
                                             c.ptr(send_base), T, top_k, x.shape[1], num_experts, self.world, self.rank,
-                                            src_stride, c.ptr(self.recv_ptrs), c.ptr(self.ridx_ptrs), self.cap_rows,
-                                            c.ptr(slot_dst), c.ptr(self.status), c.stream_ptr(x.device))
+                                            src_stride, c.ptr(self.recv_ptrs), c.ptr(self.ridx_ptrs),
+                                            c.ptr(self.home_ptrs), self.cap_rows, c.ptr(slot_dst), c.ptr(self.status), c.stream_ptr(x.device))
         c.check(rc, "mq_ep_dispatch_unique")
         c.count_launches(2 if T else 0)
         return slot_dst

@@ -31,8 +31,9 @@ def test_unique_rows_index(T, K, E, G):
     assert np.array_equal(uniq.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("unique", [True, False])
 @pytest.mark.parametrize("G,T,K,E,H", [(2, 37, 2, 4, 64), (4, 300, 4, 16, 256), (8, 500, 8, 64, 512)])
-def test_dispatch_unique_delivers_every_slot(G, T, K, E, H):
+def test_dispatch_delivers_every_slot(G, T, K, E, H, unique):
     c = _cabi
     lib = c.load()
     st = c.stream_ptr(DEV)
@@ -44,7 +45,8 @@ def test_dispatch_unique_delivers_every_slot(G, T, K, E, H):
            for _ in range(G)]
     recv = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(G)]
     ridx = [torch.full((cap,), -1, dtype=torch.int32, device=DEV) for _ in range(G)]
-    recv_ptrs, ridx_ptrs = _ptrs(recv), _ptrs(ridx)
+    home = [torch.full((cap,), -1, dtype=torch.int32, device=DEV) for _ in range(G)]
+    recv_ptrs, ridx_ptrs, home_ptrs = _ptrs(recv), _ptrs(ridx), _ptrs(home)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     plans = [moe_permute_plan(ids[r], E, want_int64_offsets=False) for r in range(G)]
     counts = torch.stack([p[2][1:] - p[2][:-1] for p in plans]).contiguous()          # [G, E]
@@ -52,30 +54,68 @@ def test_dispatch_unique_delivers_every_slot(G, T, K, E, H):
     for r in range(G):
         perm, inv, off32, _ = plans[r]
         send_base = torch.empty(E, dtype=torch.int32, device=DEV)
-        seg = torch.empty(E + 1, dtype=torch.int32, device=DEV)
-        c.check(lib.mq_ep_plan(c.ptr(counts), G, r, E, c.ptr(send_base), c.ptr(seg), None, 0, None, st), "plan")
+        seg = torch.empty(el + 1, dtype=torch.int32, device=DEV)
+        c.check(lib.mq_ep_plan(c.ptr(counts), G, r, E, c.ptr(send_base), c.ptr(seg), st), "plan")
         segs.append(seg.cpu())
-        uniq = torch.empty(T, G, dtype=torch.int32, device=DEV)
-        c.check(lib.mq_ep_unique_rows(c.ptr(ids[r]), T, K, E, G, c.ptr(uniq), st), "unique")
         slot_dst = torch.empty(T * K, dtype=torch.int32, device=DEV)
-        c.check(lib.mq_ep_dispatch_unique(c.ptr(xs[r]), c.dtype_code(xs[r]), c.ptr(uniq), c.ptr(perm), c.ptr(off32),
-                                          c.ptr(send_base), T, K, H, E, G, r, T, c.ptr(recv_ptrs), c.ptr(ridx_ptrs),
-                                          cap, c.ptr(slot_dst), c.ptr(status), st), "dispatch_unique")
+        if unique:
+            uniq = torch.empty(T, G, dtype=torch.int32, device=DEV)
+            c.check(lib.mq_ep_unique_rows(c.ptr(ids[r]), T, K, E, G, c.ptr(uniq), st), "unique")
+            c.check(lib.mq_ep_dispatch_unique(c.ptr(xs[r]), c.dtype_code(xs[r]), c.ptr(uniq), c.ptr(perm),
+                                              c.ptr(off32), c.ptr(send_base), T, K, H, E, G, r, T, c.ptr(recv_ptrs),
+                                              c.ptr(ridx_ptrs), c.ptr(home_ptrs), cap, c.ptr(slot_dst),
+                                              c.ptr(status), st), "dispatch_unique")
+        else:
+            c.check(lib.mq_ep_dispatch(c.ptr(xs[r]), c.dtype_code(xs[r]), c.ptr(perm), c.ptr(off32), c.ptr(send_base),
+                                       T * K, K, H, E, G, r, c.ptr(recv_ptrs), c.ptr(home_ptrs), cap, c.ptr(slot_dst),
+                                       c.ptr(status), st), "dispatch")
+        # slot_dst names the owner and the slot of every sorted position
+        sd = slot_dst.cpu().long()
+        owner = torch.repeat_interleave(torch.arange(E), (off32[1:] - off32[:-1]).cpu().long()) // el
+        assert torch.equal(sd // cap, owner)
     torch.cuda.synchronize()
     assert status.item() == 0
-    # receive side of rank d: group (s, j) holds, in sorted order, the rows of rank s's tokens routed to expert d*el+j
+    # receive side of rank d: expert j's group holds rank 0's slots, then rank 1's, ..., each in sorted order
     for d in range(G):
-        table = ridx[d].cpu()
-        buf = recv[d].cpu()
+        table, homes, buf = ridx[d].cpu(), home[d].cpu(), recv[d].cpu()
         pos = 0
-        for s in range(G):
-            perm_s, off_s = plans[s][0].cpu(), plans[s][2].cpu()
-            for j in range(el):
-                e = d * el + j
-                assert int(segs[d][s * el + j]) == pos
-                toks = perm_s[int(off_s[e]):int(off_s[e + 1])] // K
-                rows = table[pos:pos + toks.numel()].long()
-                assert bool(((rows >= s * T) & (rows < (s + 1) * T)).all())
-                assert torch.equal(buf[rows], xs[s].cpu()[toks.long()])
-                pos += toks.numel()
+        for j in range(el):
+            e = d * el + j
+            assert int(segs[d][j]) == pos
+            for s in range(G):
+                perm_s, off_s = plans[s][0].cpu(), plans[s][2].cpu()
+                lo, hi = int(off_s[e]), int(off_s[e + 1])
+                toks = (perm_s[lo:hi] // K).long()
+                n = hi - lo
+                want_home = (s << 26) | torch.arange(lo, hi)
+                assert torch.equal(homes[pos:pos + n].long(), want_home)
+                if unique:
+                    rows = table[pos:pos + n].long()
+                    assert bool(((rows >= s * T) & (rows < (s + 1) * T)).all())
+                    assert torch.equal(buf[rows], xs[s].cpu()[toks])
+                else:
+                    assert torch.equal(buf[pos:pos + n], xs[s].cpu()[toks])
+                pos += n
         assert int(segs[d][-1]) == pos
+
+
+def test_exchange_plan_single_rank_matches_plan():
+    """G = 1: the fused counts/barrier/plan launch meets only itself and must give the plain plan."""
+    c = _cabi
+    lib = c.load()
+    st = c.stream_ptr(DEV)
+    E, T, K = 32, 200, 4
+    g = torch.Generator().manual_seed(5)
+    ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    _, _, off32, _ = moe_permute_plan(ids, E, want_int64_offsets=False)
+    counts = torch.zeros(E, dtype=torch.int32, device=DEV)
+    sig = torch.zeros(32, dtype=torch.int32, device=DEV)
+    epoch = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    sb, seg = (torch.empty(E, dtype=torch.int32, device=DEV), torch.empty(E + 1, dtype=torch.int32, device=DEV))
+    for _ in range(2):                                    # the epoch advances; a second call must pass as well
+        c.check(lib.mq_ep_exchange_plan(c.ptr(off32), E, 1, 0, c.ptr(_ptrs([counts])), c.ptr(_ptrs([sig])),
+                                        c.ptr(epoch), c.ptr(sb), c.ptr(seg), c.ptr(status), st), "exchange_plan")
+    assert status.item() == 0 and epoch.item() == 2
+    assert torch.equal(counts, off32[1:] - off32[:-1])
+    assert torch.equal(seg, off32) and torch.equal(sb, off32[:-1])

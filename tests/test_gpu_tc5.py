@@ -95,9 +95,9 @@ def test_tc5_swiglu_with_fused_gather(T, K, E, I, H):
 
 @pytest.mark.parametrize("counts,N,Kd", [([5, 0, 130, 17], 128, 64), ([260, 31, 0, 300, 1, 90], 256, 512),
                                          ([700, 3, 256, 255, 257, 0, 16, 48], 2048, 768)])
-def test_tc5_scatter_gemm_writes_each_group_at_its_own_address(counts, N, Kd):
-    """Per-group destinations: the rows of every group land from the group's own address on (groups placed
-    in reverse order in one buffer, with a guard row between them), with the bits of the plain call."""
+def test_tc5_scatter_gemm_writes_each_row_at_its_own_address(counts, N, Kd):
+    """Per-row destinations: every output row lands at the row its code names, in one of three buffers,
+    with the bits of the plain call; rows no code names stay untouched."""
     from mini_qwen_b200.kernels.moe_grouped_gemm import moe_grouped_gemm_scatter
     E = len(counts)
     S = sum(counts)
@@ -106,17 +106,16 @@ def test_tc5_scatter_gemm_writes_each_group_at_its_own_address(counts, N, Kd):
     w = (torch.randn(E, N, Kd, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     off = offsets_from_counts(counts).to(torch.int32).to(DEV)
     plain = moe_grouped_gemm(a, w, off)
-    buf = torch.full((S + E, N), 7.0, dtype=torch.bfloat16, device=DEV)
-    starts, row = [0] * E, 0
-    for e in reversed(range(E)):
-        starts[e] = row
-        row += counts[e] + 1                                   # one guard row after every group
-    addr = torch.tensor([buf.data_ptr() + s * N * 2 for s in starts], dtype=torch.int64, device=DEV)
+    rows_per_buf = S + 3
+    bufs = [torch.full((rows_per_buf, N), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+    bases = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
+    which = torch.randint(0, 3, (S,), generator=g)
+    place = torch.randperm(rows_per_buf, generator=g)[:S]            # distinct rows, so no two codes collide
+    code = ((which << 26) | place).to(torch.int32).to(DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    moe_grouped_gemm_scatter(a, w, off, addr, status=status)
+    moe_grouped_gemm_scatter(a, w, off, code, bases, status=status)
     assert status.item() == 0
-    lo = 0
-    for e in range(E):
-        assert torch.equal(buf[starts[e]:starts[e] + counts[e]], plain[lo:lo + counts[e]])
-        assert bool((buf[starts[e] + counts[e]] == 7.0).all())          # guard row untouched
-        lo += counts[e]
+    got = torch.stack([bufs[int(b)][int(r)] for b, r in zip(which, place)])
+    assert torch.equal(got, plain)
+    written = sum(int((b != 7.0).any(dim=1).sum()) for b in bufs)
+    assert written <= S                                               # nothing outside the named rows
