@@ -167,31 +167,51 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 constexpr int RM_TM = 32, RM_TE = 128, RM_THREADS = 256;
+constexpr int RM_BK = 64;                       // k per pipeline stage: 128-byte rows in shared memory
+constexpr int RM_STAGES = 3;                    // 60 KB per CTA: three CTAs per SM
+constexpr int RM_ROWS = RM_TM + RM_TE;          // token rows, then expert rows
+constexpr int RM_STAGE_BYTES = RM_ROWS * RM_BK * 2;   // 20 KB
+constexpr int RM_SMEM_BYTES = RM_STAGES * RM_STAGE_BYTES;
 
+__device__ __forceinline__ void rm_cp_async16(uint32_t dst, const void* src, bool ok) {
+  const int n = ok ? 16 : 0;                    // 0 bytes read: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+
+// The operands travel global -> shared memory in 64-k stages by cp.async (3 stages per CTA, three CTAs per SM),
+// 16-byte pieces XOR-swizzled by row so that the fragment loads are conflict-free.  The arithmetic is
+// the one described above, in the same order for every token, whatever the staging.
 __global__ void __launch_bounds__(RM_THREADS)
 router_logits_mma(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, int is_bf16,
                   int64_t T, int64_t H, int64_t E, int64_t k_per_slice, float* __restrict__ logits) {
+  extern __shared__ __align__(128) uint8_t rm_smem[];
+  const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(rm_smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, kq = lane & 3;
   const int wm = warp & 1, wn = warp >> 1;
-  const int64_t t0 = (int64_t)blockIdx.x * RM_TM + 16 * wm;
-  const int64_t e0 = (int64_t)blockIdx.y * RM_TE + 32 * wn;
+  const int64_t tb = (int64_t)blockIdx.x * RM_TM;           // first token of the CTA
+  const int64_t eb = (int64_t)blockIdx.y * RM_TE;           // first expert of the CTA
   const int64_t k_lo = (int64_t)blockIdx.z * k_per_slice;
   const int64_t k_hi = min(k_lo + k_per_slice, H);
   const bool bf = is_bf16 != 0;
+  const int nstage = k_lo < k_hi ? (int)((k_hi - k_lo + RM_BK - 1) / RM_BK) : 0;
 
-  const int64_t ra = t0 + g, rb = t0 + g + 8;
-  const bool ra_ok = ra < T, rb_ok = rb < T;
-  const uint16_t* xa = x + (size_t)(ra_ok ? ra : 0) * H + 8 * kq;
-  const uint16_t* xb = x + (size_t)(rb_ok ? rb : 0) * H + 8 * kq;
-  const uint16_t* wp[4];
-  bool w_ok[4];
+  // loader: 160 rows x 8 pieces of 16 bytes per stage = 1280 pieces, 5 per thread
+  auto load_stage = [&](int st) {
+    const int64_t k0 = k_lo + (int64_t)st * RM_BK;
+    const uint32_t base = smem0 + (uint32_t)(st % RM_STAGES) * RM_STAGE_BYTES;
 #pragma unroll
-  for (int n = 0; n < 4; ++n) {
-    const int64_t e = e0 + 8 * n + g;
-    w_ok[n] = e < E;
-    wp[n] = w + (size_t)(w_ok[n] ? e : 0) * H + 8 * kq;
-  }
+    for (int i = 0; i < (RM_ROWS * 8) / RM_THREADS; ++i) {
+      const int piece = threadIdx.x + i * RM_THREADS;
+      const int row = piece >> 3, c = piece & 7;
+      const int64_t k = k0 + 8 * c;
+      const bool is_tok = row < RM_TM;
+      const int64_t r = is_tok ? tb + row : eb + (row - RM_TM);
+      const bool ok = (is_tok ? r < T : r < E) && k < k_hi;   // H % 32 == 0 and slices are multiples of 128
+      const uint16_t* src = (is_tok ? x : w) + (size_t)(ok ? r : 0) * H + (ok ? k : 0);
+      rm_cp_async16(base + (uint32_t)row * 128u + (uint32_t)((c ^ (row & 7)) << 4), src, ok);
+    }
+  };
 
   float master[4][4], part[4][4];
 #pragma unroll
@@ -199,41 +219,52 @@ router_logits_mma(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w
 #pragma unroll
     for (int i = 0; i < 4; ++i) { master[n][i] = 0.0f; part[n][i] = 0.0f; }
 
-  const uint4 zero4 = make_uint4(0, 0, 0, 0);
-  // the loads of block k+32 are issued before the MMAs of block k
-  uint4 va = zero4, vb = zero4, vw[4] = {zero4, zero4, zero4, zero4};
-  auto fetch = [&](int64_t k, uint4& a, uint4& b, uint4 (&wv)[4]) {
-    a = ra_ok ? __ldg(reinterpret_cast<const uint4*>(xa + k)) : zero4;
-    b = rb_ok ? __ldg(reinterpret_cast<const uint4*>(xb + k)) : zero4;
 #pragma unroll
-    for (int n = 0; n < 4; ++n) wv[n] = w_ok[n] ? __ldg(reinterpret_cast<const uint4*>(wp[n] + k)) : zero4;
-  };
-  if (k_lo < k_hi) fetch(k_lo, va, vb, vw);
+  for (int st = 0; st < RM_STAGES - 1; ++st) {
+    if (st < nstage) load_stage(st);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  const int row_a = 16 * wm + g, row_b = row_a + 8;         // token rows of this lane's fragments
   int in_chunk = 0;
-  for (int64_t k = k_lo; k < k_hi; k += 32) {
-    uint4 na = zero4, nb = zero4, nw[4] = {zero4, zero4, zero4, zero4};
-    if (k + 32 < k_hi) fetch(k + 32, na, nb, nw);
+  for (int st = 0; st < nstage; ++st) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(RM_STAGES - 2) : "memory");
+    __syncthreads();                                        // stage st has landed; stage st-1 is free
+    if (st + RM_STAGES - 1 < nstage) load_stage(st + RM_STAGES - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const uint8_t* base = rm_smem + (st % RM_STAGES) * RM_STAGE_BYTES;
+    const int64_t k0 = k_lo + (int64_t)st * RM_BK;
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      mma16816(part[n], va.x, vb.x, va.y, vb.y, vw[n].x, vw[n].y, bf);
-      mma16816(part[n], va.z, vb.z, va.w, vb.w, vw[n].z, vw[n].w, bf);
+    for (int h = 0; h < 2; ++h) {                           // two 32-k blocks per stage
+      if (k0 + 32 * h < k_hi) {
+        const int c = 4 * h + kq;
+        const uint4 va = *reinterpret_cast<const uint4*>(base + row_a * 128 + ((c ^ (row_a & 7)) << 4));
+        const uint4 vb = *reinterpret_cast<const uint4*>(base + row_b * 128 + ((c ^ (row_b & 7)) << 4));
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          const int row_w = RM_TM + 32 * wn + 8 * n + g;
+          const uint4 vw = *reinterpret_cast<const uint4*>(base + row_w * 128 + ((c ^ (row_w & 7)) << 4));
+          mma16816(part[n], va.x, vb.x, va.y, vb.y, vw.x, vw.y, bf);
+          mma16816(part[n], va.z, vb.z, va.w, vb.w, vw.z, vw.w, bf);
+        }
+        if (++in_chunk == 4) {          // 128 k summed in the tensor core: fold into the fp32 master
+          in_chunk = 0;
+#pragma unroll
+          for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { master[n][i] += part[n][i]; part[n][i] = 0.0f; }
+        }
+      }
     }
-    if (++in_chunk == 4) {          // 128 k summed in the tensor core: fold into the fp32 master
-      in_chunk = 0;
-#pragma unroll
-      for (int n = 0; n < 4; ++n)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { master[n][i] += part[n][i]; part[n][i] = 0.0f; }
-    }
-    va = na; vb = nb;
-#pragma unroll
-    for (int n = 0; n < 4; ++n) vw[n] = nw[n];
   }
 #pragma unroll
   for (int n = 0; n < 4; ++n)
 #pragma unroll
     for (int i = 0; i < 4; ++i) master[n][i] += part[n][i];
 
+  const int64_t ra = tb + row_a, rb = tb + row_b;
+  const bool ra_ok = ra < T, rb_ok = rb < T;
+  const int64_t e0 = eb + 32 * wn;
   float* dst = logits + (size_t)blockIdx.z * T * E;
 #pragma unroll
   for (int n = 0; n < 4; ++n) {
@@ -449,7 +480,8 @@ extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_d
     dim3 grid((unsigned)((T + R_TM - 1) / R_TM), (unsigned)((E + R_TE - 1) / R_TE), (unsigned)slices);
     if (mma) {
       // same tile shape as the SIMT kernel (32 tokens x 128 experts), so the grid carries over
-      router_logits_mma<<<grid, RM_THREADS, 0, st>>>(reinterpret_cast<const uint16_t*>(x),
+      cudaFuncSetAttribute(router_logits_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, RM_SMEM_BYTES);
+      router_logits_mma<<<grid, RM_THREADS, RM_SMEM_BYTES, st>>>(reinterpret_cast<const uint16_t*>(x),
           reinterpret_cast<const uint16_t*>(w), x_dtype == MQ_BF16, T, H, E, k_per_slice, logits_ws);
     } else {
       router_logits_tiled<<<grid, R_THREADS, 0, st>>>(x, x_dtype, w, w_dtype, T, H, E, k_per_slice, vec_ok, logits_ws);
