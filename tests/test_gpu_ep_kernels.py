@@ -113,8 +113,9 @@ def test_exchange_plan_single_rank_matches_plan():
     epoch = torch.zeros(1, dtype=torch.int32, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     sb, seg = (torch.empty(E, dtype=torch.int32, device=DEV), torch.empty(E + 1, dtype=torch.int32, device=DEV))
+    counts_ptrs, sig_ptrs = _ptrs([counts]), _ptrs([sig])  # kept alive: the launches read them asynchronously
     for _ in range(2):                                    # the epoch advances; a second call must pass as well
-        c.check(lib.mq_ep_exchange_plan(c.ptr(off32), E, 1, 0, c.ptr(_ptrs([counts])), c.ptr(_ptrs([sig])),
+        c.check(lib.mq_ep_exchange_plan(c.ptr(off32), E, 1, 0, c.ptr(counts_ptrs), c.ptr(sig_ptrs),
                                         c.ptr(epoch), c.ptr(sb), c.ptr(seg), c.ptr(status), st), "exchange_plan")
     assert status.item() == 0 and epoch.item() == 2
     assert torch.equal(counts, off32[1:] - off32[:-1])
