@@ -373,17 +373,21 @@ def run_ours(args):
     roofline = None
     if gemm1_ms:
         achieved = gemm1_flops / (gemm1_ms * 1e-3) / 1e12
-        roofline = {"bound": "tensor", "kernel": "grouped gate/up GEMM + SwiGLU", "achieved": achieved,
-                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+        # algorithmic bytes of one launch: this rank's gate/up weights once, every token row once, h once
+        alg_bytes = (E // world) * 2 * I * H * 2 + T * H * 2 + S * I * 2
+        roofline = {"bound": "tensor", "kernel": "grouped gate/up GEMM + SwiGLU (rows gathered in the kernel)",
+                    "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["bf16_tflops"],
                     "peak_source": f"{peaks['source']} burst bf16 GEMM",
                     # dram__bytes_read.sum + dram__bytes_write.sum of this kernel at this workload, one ncu
-                    # capture (profiles/grouped_gemm_tc5_c2.md); algorithmic bytes are 989e6
-                    "traffic": 1006.1e6 if world == 1 else None,
-                    "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms,
-                    # the layer is on the ridge: the same launch seen from the HBM side (algorithmic bytes:
-                    # 805 MB weights + 134 MB rows + 50 MB h)
-                    "hbm": {"achieved": 989.0e6 / (gemm1_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                            "frac": 989.0e6 / (gemm1_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
+                    # capture (profiles/grouped_gemm_tc5_c2.md): 892.0 MB read + 45.4 MB written
+                    "traffic": 937.3e6 if world == 1 else None,
+                    "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms}
+        if world == 1:
+            # the layer is on the ridge: the same launch seen from the HBM side
+            gbs = alg_bytes / (gemm1_ms * 1e-3) / 1e9
+            roofline["hbm"] = {"achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                               "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes": alg_bytes}
 
     cpu_base = None
     if world == 1 and not args.no_cpu_baseline:
