@@ -195,6 +195,30 @@ int mq_w4a16_grouped_swiglu(const void* x,
                             int64_t S, int64_t E, int64_t weight_period, int64_t I, int64_t H, int64_t group_size,
                             void* h, void* stream);
 
+/* The same two W4A16 operations on the tcgen05 tensor cores, for decode-size groups (any group size
+ * is correct; it is tuned for groups of at most 32 rows).  The packed weights stream in by TMA in
+ * the checkpoint layout, are turned into bf16 in registers and written to tensor memory, from where
+ * the MMA reads them; the activations must be PREPARED first:
+ * mq_w4a16_tc_prep: x bf16 [T,Kd] -> xp bf16 [S,Kd], row r = x[perm[r]/top_k] (perm NULL: x[r],
+ *   S = T) with the k order 0,4,1,5,2,6,3,7 inside every 8 when `shuffle` != 0, and
+ *   xs fp32 [S,32]: xs[r][g] = sum of the row over quantisation group g (Kd <= 4096).  xp may be
+ *   NULL (sums only: the output of mq_w4a16_tc_swiglu is already in the shuffled order).
+ * mq_w4a16_tc_swiglu: h_shuffled[r,:] = the fused gate/up + SwiGLU row of mq_w4a16_grouped_swiglu with
+ *   its columns in the shuffled k order, ready to be the xp of the down projection.
+ * mq_w4a16_tc_gemm: out[r,:] as mq_w4a16_grouped_gemm, natural column order.
+ * group_size == 128, Kd % 128 == 0, N % 128 == 0 (MQ_ERR_UNSUPPORTED_SHAPE otherwise). */
+int mq_w4a16_tc_prep(const void* x, const int32_t* perm, int64_t top_k, int64_t S, int64_t Kd,
+                     int shuffle, void* xp, float* xs, void* stream);
+int mq_w4a16_tc_gemm(const void* xp, const float* xs, const int32_t* qweight, const void* scales,
+                     const int32_t* qzeros, const int32_t* offsets, int64_t S, int64_t E,
+                     int64_t weight_period, int64_t N, int64_t Kd, int64_t group_size, void* out,
+                     int32_t* d_status, void* stream);
+int mq_w4a16_tc_swiglu(const void* xp, const float* xs,
+                       const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
+                       const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
+                       const int32_t* offsets, int64_t S, int64_t E, int64_t weight_period, int64_t I,
+                       int64_t H, int64_t group_size, void* h_shuffled, int32_t* d_status, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Expert parallelism over peer memory (no counterpart in the reference, which is single-GPU).
  * G ranks, rank r owns experts [r*E/G, (r+1)*E/G).  Every rank provides a receive buffer and an

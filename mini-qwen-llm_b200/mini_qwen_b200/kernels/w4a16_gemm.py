@@ -92,3 +92,66 @@ def w4a16_gemm(
         offsets = _single_offsets[key] = torch.tensor([0, M], dtype=torch.int32, device=x.device)
     return w4a16_grouped_gemm(x, qweight.contiguous().unsqueeze(0), scales.contiguous().unsqueeze(0),
                               qzeros.contiguous().unsqueeze(0), offsets, group_size, zero_init=False)
+
+
+# ---- tcgen05 path for decode-size groups ------------------------------------------------------
+
+def w4a16_tc_supported(hidden: int, out_features: int, group_size: int) -> bool:
+    """Shapes the tensor-memory kernel covers: group 128, K a multiple of 128 up to 4096, N a multiple of 128."""
+    return group_size == 128 and hidden % 128 == 0 and hidden <= 4096 and out_features % 128 == 0
+
+
+def w4a16_tc_prep(x: torch.Tensor, perm: torch.Tensor | None = None, top_k: int = 1, shuffle: bool = True,
+                  want_rows: bool = True):
+    """Activations for the tensor-memory kernels: (xp, xs).  xp [S, K] = the (optionally gathered) rows with
+    the k order 0,4,1,5,2,6,3,7 inside every 8; xs fp32 [S, 32] = per-row sums over every 128 k."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2
+    x = x.contiguous()
+    S = perm.numel() if perm is not None else x.shape[0]
+    K = x.shape[1]
+    xp = torch.empty(S, K, dtype=torch.bfloat16, device=x.device) if want_rows else None
+    xs = torch.empty(S, 32, dtype=torch.float32, device=x.device)
+    rc = _cabi.load().mq_w4a16_tc_prep(_cabi.ptr(x), _cabi.ptr(perm) if perm is not None else None, top_k, S, K,
+                                       1 if shuffle else 0, _cabi.ptr(xp) if want_rows else None, _cabi.ptr(xs),
+                                       _cabi.stream_ptr(x.device))
+    _cabi.check(rc, "mq_w4a16_tc_prep")
+    _cabi.count_launches(1 if S else 0)
+    return xp, xs
+
+
+def w4a16_tc_swiglu(xp, xs, gate, up, expert_offsets, group_size: int = 128, status: torch.Tensor | None = None):
+    """Fused gate/up + SwiGLU on prepared activations; the result's columns are in the shuffled k order
+    (it is the ``xp`` of the down projection)."""
+    E = gate[0].shape[0]
+    K, N = _check_w4(xp, *gate, group_size, E)
+    _check_w4(xp, *up, group_size, E)
+    groups = expert_offsets.numel() - 1
+    S = xp.shape[0]
+    h = torch.empty(S, N, dtype=torch.bfloat16, device=xp.device)
+    rc = _cabi.load().mq_w4a16_tc_swiglu(_cabi.ptr(xp), _cabi.ptr(xs), _cabi.ptr(gate[0]), _cabi.ptr(gate[1]),
+                                         _cabi.ptr(gate[2]), _cabi.ptr(up[0]), _cabi.ptr(up[1]), _cabi.ptr(up[2]),
+                                         _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size, _cabi.ptr(h),
+                                         _cabi.ptr(status) if status is not None else None,
+                                         _cabi.stream_ptr(xp.device))
+    _cabi.check(rc, "mq_w4a16_tc_swiglu")
+    _cabi.count_launches(1 if S else 0)
+    return h
+
+
+def w4a16_tc_gemm(xp, xs, qweight, scales, qzeros, expert_offsets, group_size: int = 128,
+                  status: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One W4A16 projection per group on prepared activations; natural column order."""
+    E = qweight.shape[0]
+    K, N = _check_w4(xp, qweight, scales, qzeros, group_size, E)
+    groups = expert_offsets.numel() - 1
+    S = xp.shape[0]
+    if out is None:
+        out = torch.empty(S, N, dtype=torch.bfloat16, device=xp.device)
+    assert out.is_contiguous() and tuple(out.shape) == (S, N) and out.dtype == torch.bfloat16
+    rc = _cabi.load().mq_w4a16_tc_gemm(_cabi.ptr(xp), _cabi.ptr(xs), _cabi.ptr(qweight), _cabi.ptr(scales),
+                                       _cabi.ptr(qzeros), _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size,
+                                       _cabi.ptr(out), _cabi.ptr(status) if status is not None else None,
+                                       _cabi.stream_ptr(xp.device))
+    _cabi.check(rc, "mq_w4a16_tc_gemm")
+    _cabi.count_launches(1 if S else 0)
+    return out

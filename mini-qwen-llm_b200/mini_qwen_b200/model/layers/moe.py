@@ -20,7 +20,8 @@ from ...kernels.moe_grouped_gemm import (gather_swiglu_supported, moe_grouped_ge
 from ...kernels.moe_permute import gather_rows, moe_permute_plan
 from ...kernels.moe_router import moe_router
 from ...kernels.moe_unpermute import unpermute_combine
-from ...kernels.w4a16_gemm import w4a16_grouped_gemm, w4a16_grouped_swiglu
+from ...kernels.w4a16_gemm import (w4a16_grouped_gemm, w4a16_grouped_swiglu, w4a16_tc_gemm, w4a16_tc_prep,
+                                     w4a16_tc_supported, w4a16_tc_swiglu)
 from ... import parallel
 from .linear_w4a16 import LinearW4A16
 
@@ -75,6 +76,9 @@ class Qwen3MoEBlock(nn.Module):
         # "unique": a token row crosses NVLink once per destination rank and the owner's gate/up kernel
         # gathers through a slot table; "slots": one copy per slot (W4A16 experts, more than 8 ranks)
         self.ep_dispatch = "unique"
+        # W4A16 experts: "tc" = tcgen05 kernel with the weights dequantised into tensor memory (decode
+        # batches), "mma" = the mma.sync stream kernel, "auto" = by the number of slots per expert
+        self.w4_kernel = "mma"
         self._peer = None
         self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
         self.ep_rank = 0 if ep_group is None else torch.distributed.get_rank(ep_group)
@@ -193,6 +197,12 @@ class Qwen3MoEBlock(nn.Module):
             h = run("grouped_swiglu", moe_grouped_swiglu_gather, x2d, perm, K, st["w13"], off32, status=status)
             out_perm = run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False, status=status)
             return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K).reshape(shape)
+        if self.ep_size == 1 and st["w4"] and self._w4_tc(st, T * K):
+            # decode-size groups: weights dequantised into tensor memory, activations prepared once
+            status = self._status_word(x2d.device)
+            xp, xs = run("w4_prep", w4a16_tc_prep, x2d, perm, K)
+            out_perm = self._experts_w4_tc(st, xp, xs, off32, status)
+            return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K).reshape(shape)
         plan = None
         if self.ep_size > 1:
             all_counts = parallel.gather_counts(off32[1:] - off32[:-1], self.ep_group)
@@ -219,6 +229,26 @@ class Qwen3MoEBlock(nn.Module):
         status = self._status_word(rows.device)
         h = run("grouped_swiglu", moe_grouped_swiglu, rows, st["w13"], off32, zero_init=False, status=status)
         return run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False, out=out, status=status)
+
+    def _w4_tc(self, st, slots: int) -> bool:
+        """Whether the W4A16 projections run on the tensor-memory kernel (``w4_kernel``: "auto", "tc", "mma")."""
+        if self.w4_kernel == "mma":
+            return False
+        H = st["gate_proj"][0].shape[1] * 8
+        I = st["gate_proj"][0].shape[2]
+        ok = w4a16_tc_supported(H, I, st["group_size"]) and w4a16_tc_supported(I, H, st["group_size"])
+        if self.w4_kernel == "tc":
+            return ok
+        # tuned for groups of at most 32 rows: decode batches
+        return ok and slots <= 32 * st["gate_proj"][0].shape[0]
+
+    def _experts_w4_tc(self, st, xp, xs, off32, status, out=None):
+        run = self._stage
+        h = run("grouped_swiglu", w4a16_tc_swiglu, xp, xs, st["gate_proj"], st["up_proj"], off32, st["group_size"],
+                status=status)
+        _, xs2 = run("w4_sums", w4a16_tc_prep, h, shuffle=False, want_rows=False)
+        return run("grouped_down", w4a16_tc_gemm, h, xs2, *st["down_proj"], off32, st["group_size"], status=status,
+                   out=out)
 
     def _status_word(self, device) -> torch.Tensor:
         """Device status word of this block's kernels (bit 0: a bounded wait expired); allocated once."""
