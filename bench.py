@@ -114,7 +114,7 @@ def build_dense_block(lay, device, rank=0, world=1, group=None):
     return blk
 
 
-def w4a16_decode_numbers(dev, peaks, iters=200, copies=8, batches=(1, 8, 16, 64)):
+def w4a16_decode_numbers(dev, peaks, iters=200, copies=8, batches=(1, 8, 16, 64), w4_kernel=None):
     """W4A16 decode of the same layer shape: per batch size, the time of one block call under
     CUDA-graph replay, rotating over `copies` independently drawn layers so that no weight byte is
     served from L2 (a layer's active experts are 20-310 MB; 8 layers exceed the 126 MB L2 several
@@ -141,6 +141,8 @@ def w4a16_decode_numbers(dev, peaks, iters=200, copies=8, batches=(1, 8, 16, 64)
         blk._stacks = {"w4": True, "group_size": 128, "gate_proj": stack(H, I), "up_proj": stack(H, I),
                        "down_proj": stack(I, H)}
         blk._ready = lambda st=blk._stacks: st          # stacks are installed directly (random packed words)
+        if w4_kernel:
+            blk.w4_kernel = w4_kernel
         blocks.append(blk)
 
     expert_bytes = 3 * (H * I // 2) + 2 * (H // 128) * I * 2 + (I // 128) * H * 2 \
@@ -435,6 +437,8 @@ def main():
                     help="only the W4A16 decode numbers (small profiling runs); prints their JSON list")
     ap.add_argument("--decode-iters", type=int, default=200)
     ap.add_argument("--decode-batches", default="1,8,16,64")
+    ap.add_argument("--w4-kernel", default=None, choices=["auto", "tc", "mma"],
+                    help="W4A16 kernel of the decode numbers (default: the block's own choice)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -444,7 +448,7 @@ def main():
         torch.cuda.set_device(dev)
         batches = tuple(int(b) for b in args.decode_batches.split(","))
         print(json.dumps({"w4a16_decode": w4a16_decode_numbers(dev, measured_peaks(), iters=args.decode_iters,
-                                                                batches=batches)}))
+                                                                batches=batches, w4_kernel=args.w4_kernel)}))
     else:
         run_ours(args)
 

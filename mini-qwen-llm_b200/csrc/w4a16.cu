@@ -379,7 +379,6 @@ int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* o
   // few rows in total (a handful of experts hit): split K across the warps of a CTA to get enough CTAs;
   // otherwise every warp streams the whole K of its own column tile
   bool split = S <= 32;
-  if (const char* ov = getenv("MQ_W4_SPLIT")) split = ov[0] == '1';   // experiment switch
   if (swiglu) {
     if (split) launch_w4_variant<true, 4>(x, p0, p1, offsets, S, E, period, N, Kd, group, out, st);
     else launch_w4_variant<true, 1>(x, p0, p1, offsets, S, E, period, N, Kd, group, out, st);

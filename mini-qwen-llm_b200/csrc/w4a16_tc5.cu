@@ -6,7 +6,8 @@
 // The packed weights are the only large stream (0.5 byte per weight), so the kernel is built around
 // touching each int4 word once with as few instructions as possible:
 //   * output columns are the 128 TMEM lanes (M), the group's tokens are N (16 or 32), K = 16 per MMA;
-//   * the int32 words [8 k-rows x 128 columns] of a 64-k block arrive by TMA in the checkpoint layout;
+//   * the int32 words [16 k-rows x 128 columns] of one quantisation group (128 k) arrive by TMA in the
+//     checkpoint layout, together with the group's slice of the token rows: one ring stage per group;
 //   * eight dequantisation warps read one word per lane and column (conflict-free), turn it into four
 //     bf16 pairs with one shift and one logic op each ((w >> 4p) & 0x000F000F | 0x43004300 = {128+q_p,
 //     128+q_{p+4}}), and write them straight into TENSOR MEMORY (tcgen05.st), from where tcgen05.mma
@@ -19,6 +20,15 @@
 //     s * (D - (128+z) * xs) in fp32, xs = sum of x over the group (computed by the preparation kernel).
 //     The dequantised weight is never rounded.
 // Every wait is a bounded mbarrier wait; on expiry the kernel sets MQ_DEV_WAIT_EXPIRED and leaves.
+//
+// Measured on B200 (decode layer H=2048, I=768, 128 experts, batch 64: about 4 tokens per expert):
+// gate/up 120 us and down 95 us against 87 us and 42 us of the mma.sync stream kernel (w4a16.cu), so the
+// block does not use this kernel unless asked to (Qwen3MoEBlock.w4_kernel = "tc").  A timeline taken
+// with clock64 shows why: the thread that issues the MMAs needs about 65 cycles per tcgen05.mma whatever
+// its size, and an MMA of 16 tokens covers only 128 columns x 16 k = 2048 weights, so issue alone costs
+// 1000 cycles per quantisation group and tile (the dequantisation warps need the same 1000, the fold
+// warps 450, and they overlap); rotating the k steps over independent accumulators changes nothing.
+// The shape pays off only with more tokens per expert than a decode batch has.
 #include <cuda.h>
 
 #include <mutex>
@@ -29,19 +39,20 @@ namespace mq {
 namespace {
 
 constexpr int W_TM = 128;                       // output columns per sub-tile = TMEM lanes
-constexpr int W_BK = 64;                        // k per ring stage
+constexpr int W_GK = 128;                       // k per ring stage = one quantisation group
 constexpr int W_TN = 32;                        // most tokens per tile (MMA N is 16 or 32)
-constexpr int W_STAGES = 8;
-constexpr int W_WORDS_BYTES = 8 * W_TM * 4;     // 4 KB: 8 word rows x 128 columns
-constexpr int W_X_BYTES = W_TN * W_BK * 2;      // 4 KB: 32 token rows of 128 bytes, 128-byte swizzle
-constexpr int W_STAGE_BYTES = 2 * W_WORDS_BYTES + W_X_BYTES;   // 12 KB (the second word block: up projection)
+constexpr int W_STAGES = 6;
+constexpr int W_WORDS_BYTES = (W_GK / 8) * W_TM * 4;   // 8 KB: 16 word rows x 128 columns
+constexpr int W_XATOM_BYTES = W_TN * 64 * 2;    // 4 KB: 32 token rows of 64 k (128 bytes), 128-byte swizzle
+constexpr int W_X_BYTES = 2 * W_XATOM_BYTES;    // 8 KB: the two 64-k halves of the group
+constexpr int W_STAGE_BYTES = 2 * W_WORDS_BYTES + W_X_BYTES;   // 24 KB (the second word block: up projection)
 constexpr int W_XS_STRIDE = 32;                 // floats per row of the group-sum table (>= Kd / 128)
 constexpr int W_XS_BYTES = W_TN * W_XS_STRIDE * 4;             // 4 KB per tile
 constexpr int W_FOLD_WARPS = 4, W_DQ_WARPS = 8;
 constexpr int W_THREADS = (2 + W_FOLD_WARPS + W_DQ_WARPS) * 32;   // 448
 constexpr int W_SMEM_BYTES = W_STAGES * W_STAGE_BYTES + 2 * W_XS_BYTES + 1024 /*alignment*/ + 512 /*barriers*/;
-constexpr int W_TMEM_COLS = 256;                // A: columns 0..127 (2 buffers x 2 sub-tiles x 32), D: 128..255
-constexpr int W_A_COL = 0, W_D_COL = 128;
+constexpr int W_TMEM_COLS = 512;                // A: columns 0..255 (2 buffers x 2 sub-tiles x 64), D: 256..383
+constexpr int W_A_COL = 0, W_D_COL = 256;
 constexpr uint32_t W_SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t w_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -186,32 +197,32 @@ w4a16_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   const float* xs_ptr = reinterpret_cast<const float*>(ring_ptr + W_STAGES * W_STAGE_BYTES);
   const uint32_t bars = xs_smem + 2 * W_XS_BYTES;
   uint8_t* bar_mem = ring_ptr + W_STAGES * W_STAGE_BYTES + 2 * W_XS_BYTES;
+  // One tcgen05.commit per quantisation group: `done` tells the fold warps that the group's sums are in
+  // TMEM, the dequantisation warps that the A buffer may be rewritten, and (through a fold warp's arrive
+  // on raw_empty) the producer that the MMAs have read the stage's token rows.
   auto raw_full = [&](int s) { return bars + 8u * s; };
   auto raw_empty = [&](int s) { return bars + 8u * (W_STAGES + s); };
   auto a_full = [&](int b) { return bars + 8u * (2 * W_STAGES + b); };
-  auto a_empty = [&](int b) { return bars + 8u * (2 * W_STAGES + 2 + b); };
-  auto d_full = [&](int b) { return bars + 8u * (2 * W_STAGES + 4 + b); };
-  auto d_empty = [&](int b) { return bars + 8u * (2 * W_STAGES + 6 + b); };
-  auto xs_full = [&](int b) { return bars + 8u * (2 * W_STAGES + 8 + b); };
-  auto xs_empty = [&](int b) { return bars + 8u * (2 * W_STAGES + 10 + b); };
-  constexpr int MISC = 8 * (2 * W_STAGES + 12);
+  auto done = [&](int b) { return bars + 8u * (2 * W_STAGES + 2 + b); };
+  auto d_empty = [&](int b) { return bars + 8u * (2 * W_STAGES + 4 + b); };
+  auto xs_full = [&](int b) { return bars + 8u * (2 * W_STAGES + 6 + b); };
+  auto xs_empty = [&](int b) { return bars + 8u * (2 * W_STAGES + 8 + b); };
+  constexpr int MISC = 8 * (2 * W_STAGES + 10);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(bar_mem + MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + MISC + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int NWT = N / W_TM;
-  const int KB = Kd / W_BK;
-  const int G = Kd / 128;
+  const int G = Kd / W_GK;                       // quantisation groups = ring stages per tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < W_STAGES; ++s) {
       w_mbar_init(raw_full(s), 1);
-      w_mbar_init(raw_empty(s), W_DQ_WARPS + 1);       // every dequantisation warp + the MMAs that read the tokens
+      w_mbar_init(raw_empty(s), W_DQ_WARPS + 1);       // the dequantisation warps + one fold warp on behalf of the MMAs
     }
     for (int b = 0; b < 2; ++b) {
       w_mbar_init(a_full(b), W_DQ_WARPS);
-      w_mbar_init(a_empty(b), 1);
-      w_mbar_init(d_full(b), 1);
+      w_mbar_init(done(b), 1);
       w_mbar_init(d_empty(b), W_FOLD_WARPS * 32);
       w_mbar_init(xs_full(b), 1);
       w_mbar_init(xs_empty(b), W_FOLD_WARPS * 32);
@@ -249,14 +260,15 @@ w4a16_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         w_bulk_load(xs_smem + xb * W_XS_BYTES, xs + (size_t)tl.tok0 * W_XS_STRIDE, xs_bytes, xs_full(xb));
         const int n0 = tl.wt * W_TM;
         const int wrow = (tl.expert % period) * (Kd / 8);
-        for (int kb = 0; kb < KB && ok; ++kb) {
+        for (int g = 0; g < G && ok; ++g) {
           ok = w_mbar_wait(raw_empty(stage), phase ^ 1u, abort_flag, d_status);
           if (!ok) break;
           const uint32_t st = ring + stage * W_STAGE_BYTES;
           w_mbar_expect_tx(raw_full(stage), (uint32_t)(NSUB * W_WORDS_BYTES + W_X_BYTES));
-          w_tma_load_2d(st, &map_w0, raw_full(stage), n0, wrow + kb * 8);
-          if (SWIGLU) w_tma_load_2d(st + W_WORDS_BYTES, &map_w1, raw_full(stage), n0, wrow + kb * 8);
-          w_tma_load_2d(st + 2 * W_WORDS_BYTES, &map_x, raw_full(stage), kb * W_BK, tl.tok0);
+          w_tma_load_2d(st, &map_w0, raw_full(stage), n0, wrow + g * (W_GK / 8));
+          if (SWIGLU) w_tma_load_2d(st + W_WORDS_BYTES, &map_w1, raw_full(stage), n0, wrow + g * (W_GK / 8));
+          w_tma_load_2d(st + 2 * W_WORDS_BYTES, &map_x, raw_full(stage), g * W_GK, tl.tok0);
+          w_tma_load_2d(st + 2 * W_WORDS_BYTES + W_XATOM_BYTES, &map_x, raw_full(stage), g * W_GK + 64, tl.tok0);
           if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -272,78 +284,78 @@ w4a16_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       WCursor cur(offsets, E, NWT);
       int stage = 0;
       uint32_t phase = 0;
-      int kbc = 0, gc = 0;                        // k-blocks and groups issued so far
+      int gc = 0;                                 // groups issued so far
       bool ok = true;
       WTile tl;
       for (int t = blockIdx.x; ok; t += gridDim.x) {
         if (!cur.locate(t, tl)) break;
         const uint32_t idesc = w_umma_idesc(tl.n_mma);
         for (int g = 0; g < G && ok; ++g, ++gc) {
-          const int db = gc & 1;
-          ok = w_mbar_wait(d_empty(db), (uint32_t)((gc >> 1) & 1) ^ 1u, abort_flag, d_status);
+          const int b = gc & 1;
+          const uint32_t par = (uint32_t)((gc >> 1) & 1);
+          ok = w_mbar_wait(d_empty(b), par ^ 1u, abort_flag, d_status) &&      // the fold warps have read D[b]
+               w_mbar_wait(a_full(b), par, abort_flag, d_status) &&            // A[b] is written
+               w_mbar_wait(raw_full(stage), phase, abort_flag, d_status);      // the token rows have landed
           if (!ok) break;
-          const uint32_t dcol = tmem_base + W_D_COL + db * 64;
-          for (int kk = 0; kk < 2 && ok; ++kk, ++kbc) {
-            const int ab = kbc & 1;
-            ok = w_mbar_wait(a_full(ab), (uint32_t)((kbc >> 1) & 1), abort_flag, d_status) &&
-                 w_mbar_wait(raw_full(stage), phase, abort_flag, d_status);
-            if (!ok) break;
-            w_fence_after();
-            const uint64_t bd = w_umma_desc(ring + stage * W_STAGE_BYTES + 2 * W_WORDS_BYTES);
-            const uint32_t acol = tmem_base + W_A_COL + ab * 64;
+          w_fence_after();
+          const uint32_t xaddr = ring + stage * W_STAGE_BYTES + 2 * W_WORDS_BYTES;
+          const uint32_t dcol = tmem_base + W_D_COL + b * 64;
+          const uint32_t acol = tmem_base + W_A_COL + b * 128;
 #pragma unroll
-            for (int k = 0; k < W_BK / 16; ++k) {
-              const uint32_t accum = (kk | k) != 0 ? 1u : 0u;
-              w_umma_ts(dcol, acol + 8 * k, bd + 2u * k, idesc, accum);
-              if (SWIGLU) w_umma_ts(dcol + 32, acol + 32 + 8 * k, bd + 2u * k, idesc, accum);
-            }
-            w_umma_commit(a_empty(ab));            // the A buffer may be rewritten
-            w_umma_commit(raw_empty(stage));       // the token tile of the stage has been read
-            if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
+          for (int k = 0; k < W_GK / 16; ++k) {
+            const uint64_t bd = w_umma_desc(xaddr + (k >> 2) * W_XATOM_BYTES) + 2u * (k & 3);
+            const uint32_t accum = k != 0 ? 1u : 0u;
+            w_umma_ts(dcol, acol + 8 * k, bd, idesc, accum);
+            if (SWIGLU) w_umma_ts(dcol + 32, acol + 64 + 8 * k, bd, idesc, accum);
           }
-          if (!ok) break;
-          w_umma_commit(d_full(db));               // one quantisation group summed
+          w_umma_commit(done(b));
+          if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp >= 2 + W_FOLD_WARPS) {
     // ------------------------------------------------------------------ dequantisation (warps 6..13)
+    // A warp owns one TMEM lane quadrant (32 output columns) and one 64-k half of every group.
     const int quad = warp & 3;                     // TMEM lane quadrant this warp may write
-    const int khalf = (warp - (2 + W_FOLD_WARPS)) >> 2;   // which four of the eight word rows
+    const int khalf = (warp - (2 + W_FOLD_WARPS)) >> 2;
     const int col = quad * 32 + lane;              // output column inside the tile
     WCursor cur(offsets, E, NWT);
     int stage = 0;
     uint32_t phase = 0;
-    int kbc = 0;
+    int gc = 0;
     bool ok = true;
     WTile tl;
     for (int t = blockIdx.x; ok; t += gridDim.x) {
       if (!cur.locate(t, tl)) break;
-      for (int kb = 0; kb < KB && ok; ++kb, ++kbc) {
-        const int ab = kbc & 1;
+      for (int g = 0; g < G && ok; ++g, ++gc) {
+        const int b = gc & 1;
         ok = __all_sync(0xffffffffu, w_mbar_wait(raw_full(stage), phase, abort_flag, d_status) &&
-                                         w_mbar_wait(a_empty(ab), (uint32_t)((kbc >> 1) & 1) ^ 1u, abort_flag, d_status));
+                                         w_mbar_wait(done(b), (uint32_t)((gc >> 1) & 1) ^ 1u, abort_flag, d_status));
         if (!ok) break;
         w_fence_after();
         const uint8_t* st = ring_ptr + stage * W_STAGE_BYTES;
 #pragma unroll
         for (int sub = 0; sub < NSUB; ++sub) {
-          const uint32_t* words = reinterpret_cast<const uint32_t*>(st + sub * W_WORDS_BYTES) + (4 * khalf) * W_TM + col;
-          uint32_t w[4], r[16];
+          const uint32_t* words = reinterpret_cast<const uint32_t*>(st + sub * W_WORDS_BYTES) + (8 * khalf) * W_TM + col;
+          uint32_t w[8];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) w[j] = words[j * W_TM];
+          for (int j = 0; j < 8; ++j) w[j] = words[j * W_TM];
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t r[16];
 #pragma unroll
-            for (int p = 0; p < 4; ++p) r[4 * j + p] = ((w[j] >> (4 * p)) & 0x000F000Fu) | 0x43004300u;
-          w_tmem_st16(tmem_base + ((uint32_t)(quad * 32) << 16) + W_A_COL + ab * 64 + sub * 32 + khalf * 16, r);
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+              for (int p = 0; p < 4; ++p) r[4 * j + p] = ((w[4 * hh + j] >> (4 * p)) & 0x000F000Fu) | 0x43004300u;
+            w_tmem_st16(tmem_base + ((uint32_t)(quad * 32) << 16) + W_A_COL + b * 128 + sub * 64 + khalf * 32 + hh * 16, r);
+          }
         }
         w_tmem_st_wait();
         w_fence_before();
         __syncwarp();
         if (lane == 0) {
-          w_mbar_arrive(a_full(ab));
-          w_mbar_arrive(raw_empty(stage));
+          w_mbar_arrive(a_full(b));
+          w_mbar_arrive(raw_empty(stage));         // this warp has read its words of the stage
         }
         if (++stage == W_STAGES) { stage = 0; phase ^= 1u; }
       }
@@ -353,7 +365,7 @@ w4a16_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const int quad = warp & 3;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
     WCursor cur(offsets, E, NWT);
-    int gc = 0, it = 0;
+    int gc = 0, it = 0, stage = 0;
     bool ok = true;
     WTile tl;
     for (int t = blockIdx.x; ok; t += gridDim.x, ++it) {
@@ -383,16 +395,18 @@ w4a16_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           sc[NSUB - 1] = __bfloat162float(sc1[(size_t)g * N]);
           zb[NSUB - 1] = 128.0f + (float)((qz1[(size_t)g * (N / 8)] >> zshift) & 15);
         }
-        const int db = gc & 1;
-        ok = __all_sync(0xffffffffu, w_mbar_wait(d_full(db), (uint32_t)((gc >> 1) & 1), abort_flag, d_status));
+        const int b = gc & 1;
+        ok = __all_sync(0xffffffffu, w_mbar_wait(done(b), (uint32_t)((gc >> 1) & 1), abort_flag, d_status));
         if (!ok) break;
+        if (warp == 2 && lane == 0) w_mbar_arrive(raw_empty(stage));   // the MMAs have read the stage's token rows
+        if (++stage == W_STAGES) stage = 0;
         w_fence_after();
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           if (16 * half < tl.n_mma) {
             uint32_t d[NSUB][16];
 #pragma unroll
-            for (int s = 0; s < NSUB; ++s) w_tmem_ld16(lane_base + W_D_COL + db * 64 + s * 32 + 16 * half, d[s]);
+            for (int s = 0; s < NSUB; ++s) w_tmem_ld16(lane_base + W_D_COL + b * 64 + s * 32 + 16 * half, d[s]);
             w_tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -404,7 +418,7 @@ w4a16_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           }
         }
         w_fence_before();
-        w_mbar_arrive(d_empty(db));
+        w_mbar_arrive(d_empty(b));
       }
       if (!ok) break;
       w_mbar_arrive(xs_empty(xb));
@@ -540,10 +554,10 @@ static int w4_tc_launch(bool swiglu, const void* xp, const float* xs, const int3
   if (!aligned16(xp) || !aligned16(xs) || !aligned16(qw0) || (swiglu && !aligned16(qw1))) return MQ_ERR_INVALID_ARGUMENT;
   CUtensorMap map_x, map_w0, map_w1;
   const uint64_t wrows = (uint64_t)period * (uint64_t)(Kd / 8);
-  if (!w4_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xp, (uint64_t)S, (uint64_t)Kd, W_BK, W_TN,
+  if (!w4_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xp, (uint64_t)S, (uint64_t)Kd, 64, W_TN,
                  CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !w4_map_2d(&map_w0, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, qw0, wrows, (uint64_t)N, W_TM, 8, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-      !w4_map_2d(&map_w1, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, swiglu ? qw1 : qw0, wrows, (uint64_t)N, W_TM, 8,
+      !w4_map_2d(&map_w0, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, qw0, wrows, (uint64_t)N, W_TM, W_GK / 8, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+      !w4_map_2d(&map_w1, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, swiglu ? qw1 : qw0, wrows, (uint64_t)N, W_TM, W_GK / 8,
                  CU_TENSOR_MAP_SWIZZLE_NONE))
     return MQ_ERR_DRIVER_ENTRY;
   const int64_t nwt = N / W_TM;

@@ -73,3 +73,20 @@ def test_tc_projections_match_mma_sync_kernels_and_oracle(T, H, E, K, I):
         want_u = O.w4a16_linear(xe, lay.up.qweight[e], lay.up.scales[e].to(torch.bfloat16), lay.up.qzeros[e])
         h_want = (torch.nn.functional.silu(want) * want_u)
         close(h_tc[lo:hi][:, pos].cpu(), h_want)
+
+
+@pytest.mark.parametrize("T", [1, 16, 64])
+def test_block_on_the_tensor_memory_kernel_matches_reference_outputs(T):
+    """The whole W4A16 decode block with ``w4_kernel = "tc"`` against the reference's stored outputs."""
+    import cases
+    from test_gpu_block import assert_block_close, cpu, w4_block
+    lay, g = cases.config3(), cases.golden("c3")
+    blk = w4_block(lay)
+    blk.w4_kernel = "tc"
+    x = lay.x[:T].to(DEV)
+    out = blk(x)
+    assert_block_close(cpu(out), cases.from_bits(g[f"out_T{T}"], torch.bfloat16))
+    blk.w4_kernel = "mma"
+    other = blk(x)
+    close(out, other)
+    blk.check_status()
