@@ -258,11 +258,20 @@ ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict
                      : reinterpret_cast<uint4*>(peer_recv[d]) + ((int64_t)rank * src_stride + u) * vec_per_row;
     }
     const uint4* src = x + (int64_t)t * vec_per_row;
-    for (int v = lane; v < vec_per_row; v += 32) {
-      const uint4 val = __ldg(src + v);
+    // four 16-byte pieces per lane are loaded before the first store, so that a row's loads overlap
+    for (int v0 = lane; v0 < vec_per_row; v0 += 4 * 32) {
+      uint4 val[4];
 #pragma unroll
-      for (int d = 0; d < EP_MAX_G; ++d)
-        if (dst[d] != nullptr) dst[d][v] = val;
+      for (int i = 0; i < 4; ++i)
+        if (v0 + 32 * i < vec_per_row) val[i] = __ldg(src + v0 + 32 * i);
+#pragma unroll
+      for (int d = 0; d < EP_MAX_G; ++d) {
+        if (dst[d] != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (v0 + 32 * i < vec_per_row) dst[d][v0 + 32 * i] = val[i];
+        }
+      }
     }
     return;
   }
