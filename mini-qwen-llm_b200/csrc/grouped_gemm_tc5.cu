@@ -148,6 +148,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// 16 TMEM lanes x 32 columns in the fragment layout of an m16n8 accumulator, four 8-column blocks:
+// thread T holds, for block i, r[4i], r[4i+1] = lane T/4, columns 8i + 2(T%4), +1 and r[4i+2], r[4i+3] =
+// lane T/4 + 8, same columns.  With output columns in the lanes and tokens in the columns, a pair of
+// registers is two consecutive tokens of one output column: packed to bf16 it is the fragment
+// stmatrix.trans turns into token-major rows.
+__device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+// Four 8x8 bf16 matrices, stored transposed: lane L gives the address of row L%8 of matrix L/8.
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t saddr, uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};"
+               ::"r"(saddr), "r"(m0), "r"(m1), "r"(m2), "r"(m3) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(uint32_t lo_bits, uint32_t hi_bits) {
+  const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(lo_bits), __uint_as_float(hi_bits));
+  return *reinterpret_cast<const uint32_t*>(&p);
+}
+
 // SwiGLU of two accumulator pairs with the rounding points of the op-by-op bf16 path (g, silu(g), u
 // and the product are each rounded to bf16); exp and the reciprocal use the SFU approximations,
 // whose error (2^-21) is far below the bf16 rounding that follows.  Returns the packed bf16 pair.
@@ -166,16 +189,6 @@ __device__ __forceinline__ uint32_t swiglu_pair(float g0, float g1, float u0, fl
 // Barrier among the four epilogue warps that drain the same 32-token chunks (ids 1 and 2; 0 is __syncthreads).
 __device__ __forceinline__ void epi_group_sync(int group) {
   asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
-}
-
-// Puts a warp's 32 (tokens) x 32 (output columns) block of bf16 values, held as one column per lane
-// (vals[j] = packed tokens 2j, 2j+1), into the chunk's staging rows: stg + token * pitch + column * 2.
-__device__ __forceinline__ void stage_block(const uint32_t (&vals)[16], uint8_t* stg, int pitch, int col) {
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    *reinterpret_cast<uint16_t*>(stg + (2 * j) * pitch + 2 * col) = (uint16_t)(vals[j] & 0xffffu);
-    *reinterpret_cast<uint16_t*>(stg + (2 * j + 1) * pitch + 2 * col) = (uint16_t)(vals[j] >> 16);
-  }
 }
 
 // One tile of work.
@@ -454,34 +467,42 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
       tc_fence_after();
       const int f0 = tl.wt * cols_per_tile;
       const bool two = !DOUBLE && (SWIGLU || (f0 + TM < N));
-      const uint32_t taddr = tmem_base + buf * TN_MAX + ((uint32_t)(quad * 32) << 16);
       const int ntok = tl.tok_end - tl.tok0;
       for (int c = half * 32; c < tl.n_mma; c += 64) {
-        // lane = output column quad*32+lane of the sub-tile; registers = 32 consecutive tokens
-        uint32_t r0[32], r1[32], packed[16];
-        tmem_ld32(taddr + c, r0);
-        if (two) tmem_ld32(taddr + TN_MAX + c, r1);
-        tmem_ld_wait();
-        if (SWIGLU) {
+        // The accumulators leave TMEM in fragment layout (16 output columns x 32 tokens per load) and go
+        // into the staging rows through stmatrix.trans: token-major rows of 16-byte pieces (8 output
+        // columns), piece index XORed with the token's low bits so that stores and loads are conflict-free.
+        const uint32_t stg_s = smem_u32(stg);
+        const int mi = lane >> 3, ri = lane & 7;       // stmatrix: this lane addresses row ri of matrix mi
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            packed[j] = swiglu_pair(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]),
-                                    __uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-          stage_block(packed, stg, pitch, quad * 32 + lane);
-        } else {
+        for (int hl = 0; hl < 2; ++hl) {               // the two 16-lane halves of the warp's TMEM quadrant
+          const uint32_t ta = tmem_base + buf * TN_MAX + ((uint32_t)(quad * 32 + 16 * hl) << 16) + c;
+          uint32_t f0r[16], f1r[16];
+          tmem_ld_frag(ta, f0r);
+          if (two) tmem_ld_frag(ta + TN_MAX, f1r);
+          tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
-            packed[j] = *reinterpret_cast<const uint32_t*>(&p);
-          }
-          stage_block(packed, stg, pitch, quad * 32 + lane);
-          if (two) {
+          for (int sub2 = 0; sub2 < ((SWIGLU || !two) ? 1 : 2); ++sub2) {
+            uint32_t m[4][2];                           // [token octet][output-column octet]
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-              packed[j] = *reinterpret_cast<const uint32_t*>(&p);
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int a = 0; a < 2; ++a) {
+                if (SWIGLU)
+                  m[i][a] = swiglu_pair(__uint_as_float(f0r[4 * i + 2 * a]), __uint_as_float(f0r[4 * i + 2 * a + 1]),
+                                        __uint_as_float(f1r[4 * i + 2 * a]), __uint_as_float(f1r[4 * i + 2 * a + 1]));
+                else
+                  m[i][a] = sub2 == 0 ? pack_bf16x2(f0r[4 * i + 2 * a], f0r[4 * i + 2 * a + 1])
+                                      : pack_bf16x2(f1r[4 * i + 2 * a], f1r[4 * i + 2 * a + 1]);
+              }
+            // two stores of four matrices: token octets (0,1) and (2,3), each with both column octets
+#pragma unroll
+            for (int j2 = 0; j2 < 2; ++j2) {
+              const int tok = 8 * (2 * j2 + (mi >> 1)) + ri;                       // token row of the chunk
+              const int piece = (sub2 * TM + quad * 32 + 16 * hl + 8 * (mi & 1)) >> 3;   // 16-byte piece of the row
+              const uint32_t addr = stg_s + tok * pitch + ((piece ^ (tok & 7)) << 4);
+              stmatrix_x4_trans(addr, m[2 * j2][0], m[2 * j2][1], m[2 * j2 + 1][0], m[2 * j2 + 1][1]);
             }
-            stage_block(packed, stg, pitch, TM + quad * 32 + lane);
           }
         }
         const int valid = ntok - c;                    // token rows of this chunk that exist
@@ -508,7 +529,7 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
           for (int i = 0; i < 4; ++i) {
             const int row = 8 * wig + 2 * i + sub;
             if (row < valid) {
-              const uint4 v = *reinterpret_cast<const uint4*>(stg + row * pitch + piece * 16);
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + row * pitch + ((piece ^ (row & 7)) << 4));
               *reinterpret_cast<uint4*>(orow[i] + piece * 8) = v;
             }
           }
@@ -518,7 +539,7 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
           for (int i = 0; i < 8; ++i) {
             const int row = 8 * wig + i;
             if (row < valid && col_ok) {
-              const uint4 v = *reinterpret_cast<const uint4*>(stg + row * pitch + lane * 16);
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + row * pitch + ((lane ^ (row & 7)) << 4));
               *reinterpret_cast<uint4*>(orow[i] + lane * 8) = v;
             }
           }
