@@ -424,6 +424,10 @@ void launch_topk(const float* logits, int slices, const float* bias, int64_t T, 
 }  // namespace mq
 
 namespace mq {
+// Tensor-memory logits kernel (router_tc5.cu).
+bool router_tc5_covers(int x_dtype, int w_dtype, int64_t T, int64_t H, int64_t E);
+int router_logits_tc5(const void* x, const void* w, bool bf16, int64_t T, int64_t H, int64_t E, int slices,
+                      int64_t k_per_slice, float* logits, cudaStream_t st);
 namespace {
 // Batches up to this size use the one-warp-per-(expert, 8 tokens) kernel.
 constexpr int64_t R_SKINNY_MAX_T = 15;
@@ -478,7 +482,12 @@ extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_d
     int64_t k_per_slice = (H + slices - 1) / slices;
     k_per_slice = mma ? (k_per_slice + 127) / 128 * 128 : (k_per_slice + R_KC - 1) / R_KC * R_KC;
     dim3 grid((unsigned)((T + R_TM - 1) / R_TM), (unsigned)((E + R_TE - 1) / R_TE), (unsigned)slices);
-    if (mma) {
+    int tc_rc = MQ_ERR_DRIVER_ENTRY;
+    if (mma && router_tc5_covers(x_dtype, w_dtype, T, H, E))
+      tc_rc = router_logits_tc5(x, w, x_dtype == MQ_BF16, T, H, E, slices, k_per_slice, logits_ws, st);
+    if (tc_rc == MQ_OK) {
+      // logits written by the tensor-memory kernel (same slices, same 128-k chunking)
+    } else if (mma) {
       // same tile shape as the SIMT kernel (32 tokens x 128 experts), so the grid carries over
       cudaFuncSetAttribute(router_logits_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, RM_SMEM_BYTES);
       router_logits_mma<<<grid, RM_THREADS, RM_SMEM_BYTES, st>>>(reinterpret_cast<const uint16_t*>(x),
