@@ -340,6 +340,17 @@ router_logits_skinny(const void* __restrict__ x, int xdt, const void* __restrict
 }
 
 // ---------------------------------------------------------------------------------------------
+template <int NS>
+__device__ __forceinline__ float sum_slices(const float* p, size_t stride) {
+  float part[NS];
+#pragma unroll
+  for (int sl = 0; sl < NS; ++sl) part[sl] = p[sl * stride];
+  float v = part[0];
+#pragma unroll
+  for (int sl = 1; sl < NS; ++sl) v += part[sl];
+  return v;
+}
+
 // One warp per token: softmax over E logits, then K rounds of warp arg-max on (score, -id).
 template <int EPL>
 __global__ void __launch_bounds__(128)
@@ -357,12 +368,17 @@ router_softmax_topk(const float* __restrict__ logits, int slices, const float* _
     int e = lane + 32 * j;
     float v = -INFINITY;
     if (e < E) {
-      float part[16];                    // at most 16 K slices; loads first, then a fixed-order sum
-#pragma unroll
-      for (int sl = 0; sl < 16; ++sl) part[sl] = sl < slices ? logits[((size_t)sl * T + t) * E + e] : 0.0f;
-      v = part[0];
-#pragma unroll
-      for (int sl = 1; sl < 16; ++sl) if (sl < slices) v += part[sl];
+      // the K slices are summed in ascending order; the usual counts are unrolled (loads first, then adds)
+      const float* p = logits + (size_t)t * E + e;
+      const size_t stride = (size_t)T * E;
+      if (slices == 1) v = sum_slices<1>(p, stride);
+      else if (slices == 2) v = sum_slices<2>(p, stride);
+      else if (slices == 3) v = sum_slices<3>(p, stride);
+      else if (slices == 4) v = sum_slices<4>(p, stride);
+      else {
+        v = p[0];
+        for (int sl = 1; sl < slices; ++sl) v += p[sl * stride];
+      }
       if (bias != nullptr) v += bias[e];
     }
     s[j] = v;
@@ -483,7 +499,7 @@ extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_d
     k_per_slice = mma ? (k_per_slice + 127) / 128 * 128 : (k_per_slice + R_KC - 1) / R_KC * R_KC;
     dim3 grid((unsigned)((T + R_TM - 1) / R_TM), (unsigned)((E + R_TE - 1) / R_TE), (unsigned)slices);
     int tc_rc = MQ_ERR_DRIVER_ENTRY;
-    if (mma && router_tc5_covers(x_dtype, w_dtype, T, H, E))
+    if (mma && router_tc5_covers(x_dtype, w_dtype, T, H, E) && aligned16(logits_ws))
       tc_rc = router_logits_tc5(x, w, x_dtype == MQ_BF16, T, H, E, slices, k_per_slice, logits_ws, st);
     if (tc_rc == MQ_OK) {
       // logits written by the tensor-memory kernel (same slices, same 128-k chunking)

@@ -218,9 +218,20 @@ router_logits_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     const int t = t0 + quad * 32 + lane;
     if (t < T) {
       float* dst = logits + ((size_t)blockIdx.y * T + t) * E + 64 * chalf;
+      if (!ok) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i)
-        if (64 * chalf + i < E) dst[i] = ok ? master[i] : __int_as_float(0x7fc00000);
+        for (int i = 0; i < 64; ++i) master[i] = __int_as_float(0x7fc00000);
+      }
+      if ((E & 3) == 0) {                           // rows of whole 16-byte pieces (the workspace is 16-byte aligned)
+#pragma unroll
+        for (int i = 0; i < 64; i += 4)
+          if (64 * chalf + i < E)
+            *reinterpret_cast<float4*>(dst + i) = make_float4(master[i], master[i + 1], master[i + 2], master[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (64 * chalf + i < E) dst[i] = master[i];
+      }
     }
   }
 
