@@ -382,8 +382,8 @@ def run_ours(args):
                     "frac": achieved / peaks["bf16_tflops"],
                     "peak_source": f"{peaks['source']} burst bf16 GEMM",
                     # dram__bytes_read.sum + dram__bytes_write.sum of this kernel at this workload, one ncu
-                    # capture (profiles/grouped_gemm_tc5_c2.md): 892.0 MB read + 45.4 MB written
-                    "traffic": 937.3e6 if world == 1 else None,
+                    # capture (profiles/grouped_gemm_tc5_c2.md): 892.8 MB read + 45.1 MB written
+                    "traffic": 937.9e6 if world == 1 else None,
                     "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms}
         if world == 1:
             # the layer is on the ridge: the same launch seen from the HBM side
