@@ -12,7 +12,7 @@ namespace {
 
 constexpr int P_THREADS = 256;            // 8 warps
 constexpr int P_CHUNK = P_THREADS;        // slots ranked per step
-constexpr int P_SEG = 2 * P_CHUNK;        // slots per CTA in the multi-CTA plan
+constexpr int P_SEG = P_CHUNK;            // slots per CTA in the multi-CTA plan
 constexpr int P_SMALL = 8 * P_CHUNK;      // up to this many slots the whole plan runs in one CTA
 constexpr int P_MAX_E = 1024;
 
