@@ -264,9 +264,9 @@ int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, const int32_t*
                    int64_t cap_rows, int32_t* slot_dst, int32_t* d_status, void* stream);
 /* Dispatch that sends a token row once per destination RANK instead of once per slot (a token with
  * several experts on one GPU crosses NVLink once).  G <= 8.
- * mq_ep_unique_rows: topk_ids int32 [T,K] -> uniq int32 [T,G]: index of token t among this rank's
- *   tokens that have an expert on rank d, in token order, or -1 when it has none there.
- * mq_ep_dispatch_unique: row t goes to row rank*src_stride + uniq[t,d] of every rank d that needs it
+ * mq_ep_unique_rows: topk_ids int32 [T,K] -> uniq int32 [G,T] (rank-major): uniq[d,t] = index of token t
+ *   among this rank's tokens that have an expert on rank d, in token order, or -1 when it has none there.
+ * mq_ep_dispatch_unique: row t goes to row rank*src_stride + uniq[d,t] of every rank d that needs it
  *   (T <= src_stride, G*src_stride <= cap_rows), and every slot's row number goes to its slot in the
  *   owner's slot table peer_ridx_ptrs[d] (int32 [cap_rows]).  The owner runs
  *   mq_grouped_swiglu_gather with x = its receive buffer, perm = its slot table, top_k = 1.

@@ -185,52 +185,111 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm
 }
 
 // ---- dispatch with one copy per (token, destination rank) instead of one per slot.
-// A token with several of its K experts on the same GPU needs its row there once.  uniq[t, d] is the
+// A token with several of its K experts on the same GPU needs its row there once.  uniq[d, t] is the
 // index of token t among this rank's tokens that have at least one expert on rank d (token order), or
-// -1; the row travels to row rank * src_stride + uniq[t, d] of rank d's receive buffer, and every
+// -1; the row travels to row rank * src_stride + uniq[d, t] of rank d's receive buffer, and every
 // slot carries only that row number (4 bytes) to its place in the (source, local expert) order.  The
 // gate/up kernel of the owner then gathers its rows through those numbers.
 
 
+// One CTA of 1024 threads; a pass covers 4096 tokens, four consecutive ones per thread.  The per-rank
+// counts of a thread's tokens travel through the scans packed 16 bits per rank in two 64-bit words
+// (a pass never counts past 4096), so one warp scan and one scan of the 32 warp totals serve all ranks.
 __global__ void __launch_bounds__(1024)
 ep_unique_rows_kernel(const int32_t* __restrict__ ids, int T, int K, int el, int G, int32_t* __restrict__ uniq) {
-  __shared__ int s_warp[32][EP_MAX_G];
+  __shared__ unsigned long long s_warp[32][2];
   __shared__ int s_carry[EP_MAX_G];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned long long magic = 0x100000000ull / (unsigned)el + 1ull;      // id / el = (id * magic) >> 32 for id, el < 2^16
+  auto owner = [&](int id) { return (unsigned)(((unsigned long long)(unsigned)id * magic) >> 32); };
+  const bool vec = (K & 3) == 0 && ((reinterpret_cast<uintptr_t>(ids) & 15) == 0);
   if (threadIdx.x < EP_MAX_G) s_carry[threadIdx.x] = 0;
   __syncthreads();
-  for (int t0 = 0; t0 < T; t0 += 1024) {                // one token per thread and pass
-    const int t = t0 + threadIdx.x;
-    unsigned mask = 0;
-    if (t < T)
-      for (int k = 0; k < K; ++k) mask |= 1u << (ids[(int64_t)t * K + k] / el);
-    int before[EP_MAX_G];
+  for (int t0 = 0; t0 < T; t0 += 4096) {
+    const int tb = t0 + 4 * threadIdx.x;            // this thread's tokens tb .. tb+3
+    unsigned mask[4];
+    unsigned long long cnt[2] = {0ull, 0ull};
 #pragma unroll
-    for (int d = 0; d < EP_MAX_G; ++d) {
-      const unsigned votes = __ballot_sync(0xffffffffu, (mask >> d) & 1u);
-      before[d] = __popc(votes & ((1u << lane) - 1u));
-      if (lane == 0) s_warp[warp][d] = __popc(votes);
-    }
-    __syncthreads();
-    if (warp == 0) {                                    // exclusive scan of the 32 warp totals, per destination
-#pragma unroll
-      for (int d = 0; d < EP_MAX_G; ++d) {
-        const int v = s_warp[lane][d];
-        int incl = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int up = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += up;
+    for (int i = 0; i < 4; ++i) {
+      unsigned m = 0;
+      const int t = tb + i;
+      if (t < T) {
+        const int32_t* row = ids + (int64_t)t * K;
+        if (vec) {
+          for (int k = 0; k < K; k += 4) {
+            const int4 v = *reinterpret_cast<const int4*>(row + k);
+            m |= 1u << owner(v.x);
+            m |= 1u << owner(v.y);
+            m |= 1u << owner(v.z);
+            m |= 1u << owner(v.w);
+          }
+        } else {
+          for (int k = 0; k < K; ++k) m |= 1u << owner(row[k]);
         }
-        s_warp[lane][d] = s_carry[d] + incl - v;
-        __syncwarp();
-        if (lane == 31) s_carry[d] += incl;
+      }
+      mask[i] = m;
+#pragma unroll
+      for (int d = 0; d < EP_MAX_G; ++d) cnt[d >> 2] += (unsigned long long)((m >> d) & 1u) << (16 * (d & 3));
+    }
+    // inclusive warp scan of the packed counts
+    unsigned long long inc[2] = {cnt[0], cnt[1]};
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, inc[h], o);
+        if (lane >= o) inc[h] += up;
       }
     }
+    if (lane == 31) { s_warp[warp][0] = inc[0]; s_warp[warp][1] = inc[1]; }
     __syncthreads();
-    if (t < T)
-      for (int d = 0; d < G; ++d)
-        uniq[(int64_t)t * G + d] = ((mask >> d) & 1u) ? s_warp[warp][d] + before[d] : -1;
+    if (warp == 0) {                                // exclusive scan of the 32 warp totals
+      unsigned long long v[2] = {s_warp[lane][0], s_warp[lane][1]}, w[2] = {v[0], v[1]};
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const unsigned long long up = __shfl_up_sync(0xffffffffu, w[h], o);
+          if (lane >= o) w[h] += up;
+        }
+      }
+      s_warp[lane][0] = w[0] - v[0];
+      s_warp[lane][1] = w[1] - v[1];
+    }
+    __syncthreads();
+    int base[EP_MAX_G];                             // tokens before this thread's first, per rank
+#pragma unroll
+    for (int d = 0; d < EP_MAX_G; ++d) {
+      const int h = d >> 2, sh = 16 * (d & 3);
+      base[d] = s_carry[d] + (int)((s_warp[warp][h] >> sh) & 0xffffu) + (int)(((inc[h] - cnt[h]) >> sh) & 0xffffu);
+    }
+    // uniq is rank-major [G][T]: a thread's four tokens are 16 contiguous bytes per rank
+    const bool vec_out = (T & 3) == 0 && ((reinterpret_cast<uintptr_t>(uniq) & 15) == 0);
+#pragma unroll
+    for (int d = 0; d < EP_MAX_G; ++d) {
+      int v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool hit = (mask[i] >> d) & 1u;
+        v[i] = hit ? base[d] : -1;
+        base[d] += hit ? 1 : 0;
+      }
+      if (d < G) {
+        int32_t* dst = uniq + (int64_t)d * T + tb;
+        if (vec_out && tb + 3 < T) {
+          *reinterpret_cast<int4*>(dst) = make_int4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (tb + i < T) dst[i] = v[i];
+        }
+      }
+    }
+    __syncthreads();                                // every thread has read s_warp and s_carry
+    if (threadIdx.x == 1023) {                      // the last thread's running counts are the pass totals
+#pragma unroll
+      for (int d = 0; d < EP_MAX_G; ++d) s_carry[d] = base[d];
+    }
     __syncthreads();
   }
 }
@@ -249,7 +308,7 @@ ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict
     const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (t >= T) return;
     const int lane = threadIdx.x & 31;
-    const int mine = lane < G ? uniq[(int64_t)t * G + lane] : -1;
+    const int mine = lane < G ? uniq[(int64_t)lane * T + t] : -1;
     uint4* dst[EP_MAX_G];
 #pragma unroll
     for (int d = 0; d < EP_MAX_G; ++d) {
@@ -290,7 +349,7 @@ ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict
     return;
   }
   slot_dst[p] = (int32_t)(d * cap_rows + row);
-  reinterpret_cast<int32_t*>(peer_ridx[d])[row] = rank * src_stride + uniq[(int64_t)(perm[p] / K) * G + d];
+  reinterpret_cast<int32_t*>(peer_ridx[d])[row] = rank * src_stride + uniq[(int64_t)d * T + perm[p] / K];
   if (peer_home != nullptr) reinterpret_cast<int32_t*>(peer_home[d])[row] = (rank << HOME_BITS) | (int32_t)p;
 }
 
@@ -423,7 +482,7 @@ extern "C" int mq_ep_unique_rows(const int32_t* topk_ids, int64_t T, int64_t K, 
                                  int32_t* uniq, void* stream) {
   using namespace mq;
   if (T < 0 || K <= 0 || E <= 0 || G <= 0 || E % G != 0) return MQ_ERR_INVALID_ARGUMENT;
-  if (G > EP_MAX_G || T >= ((int64_t)1 << 31) / (K > G ? K : G)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (G > EP_MAX_G || E >= 65536 || T >= ((int64_t)1 << 31) / (K > G ? K : G)) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (T == 0) return MQ_OK;
   if (!topk_ids || !uniq) return MQ_ERR_INVALID_ARGUMENT;
   ep_unique_rows_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(topk_ids, (int)T, (int)K,

@@ -241,7 +241,7 @@ class PeerExchange:
         c = self._cabi
         T = x.shape[0]
         self._tables()
-        uniq = torch.empty(T, self.world, dtype=torch.int32, device=x.device)
+        uniq = torch.empty(self.world, T, dtype=torch.int32, device=x.device)
         rc = c.load().mq_ep_unique_rows(c.ptr(topk_ids32), T, top_k, num_experts, self.world, c.ptr(uniq),
                                         c.stream_ptr(x.device))
         c.check(rc, "mq_ep_unique_rows")

@@ -20,7 +20,7 @@ def _ptrs(tensors):
 def test_unique_rows_index(T, K, E, G):
     g = torch.Generator().manual_seed(T + G)
     ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
-    uniq = torch.full((T, G), -7, dtype=torch.int32, device=DEV)
+    uniq = torch.full((G, T), -7, dtype=torch.int32, device=DEV)
     c = _cabi
     c.check(c.load().mq_ep_unique_rows(c.ptr(ids.to(DEV)), T, K, E, G, c.ptr(uniq), c.stream_ptr(DEV)), "unique")
     flags = np.zeros((T, G), dtype=bool)
@@ -28,7 +28,7 @@ def test_unique_rows_index(T, K, E, G):
     for d in range(G):
         flags[:, d] = (dest == d).any(axis=1)
     want = np.where(flags, np.cumsum(flags, axis=0) - 1, -1)
-    assert np.array_equal(uniq.cpu().numpy(), want)
+    assert np.array_equal(uniq.cpu().numpy().T, want)
 
 
 @pytest.mark.parametrize("unique", [True, False])
@@ -59,7 +59,7 @@ def test_dispatch_delivers_every_slot(G, T, K, E, H, unique):
         segs.append(seg.cpu())
         slot_dst = torch.empty(T * K, dtype=torch.int32, device=DEV)
         if unique:
-            uniq = torch.empty(T, G, dtype=torch.int32, device=DEV)
+            uniq = torch.empty(G, T, dtype=torch.int32, device=DEV)
             c.check(lib.mq_ep_unique_rows(c.ptr(ids[r]), T, K, E, G, c.ptr(uniq), st), "unique")
             c.check(lib.mq_ep_dispatch_unique(c.ptr(xs[r]), c.dtype_code(xs[r]), c.ptr(uniq), c.ptr(perm),
                                               c.ptr(off32), c.ptr(send_base), T, K, H, E, G, r, T, c.ptr(recv_ptrs),
