@@ -309,14 +309,10 @@ ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict
     if (t >= T) return;
     const int lane = threadIdx.x & 31;
     const int mine = lane < G ? uniq[(int64_t)lane * T + t] : -1;
-    uint4* dst[EP_MAX_G];
-#pragma unroll
-    for (int d = 0; d < EP_MAX_G; ++d) {
-      const int u = __shfl_sync(0xffffffffu, mine, d);
-      dst[d] = u < 0 ? nullptr
-                     : reinterpret_cast<uint4*>(peer_recv[d]) + ((int64_t)rank * src_stride + u) * vec_per_row;
-    }
     const uint4* src = x + (int64_t)t * vec_per_row;
+    // consecutive tokens start with different ranks, so that the stores of the warps in flight spread
+    // over all links instead of visiting the ranks in step
+    const int rot = t & (EP_MAX_G - 1);
     // four 16-byte pieces per lane are loaded before the first store, so that a row's loads overlap
     for (int v0 = lane; v0 < vec_per_row; v0 += 4 * 32) {
       uint4 val[4];
@@ -324,11 +320,14 @@ ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict
       for (int i = 0; i < 4; ++i)
         if (v0 + 32 * i < vec_per_row) val[i] = __ldg(src + v0 + 32 * i);
 #pragma unroll
-      for (int d = 0; d < EP_MAX_G; ++d) {
-        if (dst[d] != nullptr) {
+      for (int dd = 0; dd < EP_MAX_G; ++dd) {
+        const int d = (dd + rot) & (EP_MAX_G - 1);
+        const int u = __shfl_sync(0xffffffffu, mine, d);
+        if (u >= 0) {
+          uint4* dst = reinterpret_cast<uint4*>(peer_recv[d]) + ((int64_t)rank * src_stride + u) * vec_per_row;
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            if (v0 + 32 * i < vec_per_row) dst[d][v0 + 32 * i] = val[i];
+            if (v0 + 32 * i < vec_per_row) dst[v0 + 32 * i] = val[i];
         }
       }
     }
