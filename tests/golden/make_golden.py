@@ -124,7 +124,7 @@ def run_w4(ref, name, lay, Ts):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a mini-qwen-llm checkout (the reference)")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
