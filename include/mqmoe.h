@@ -73,11 +73,14 @@ int mq_router_topk(const void* x, int x_dtype, const void* w, int w_dtype, const
  * Meant for callers that cannot give this library a workspace: code that runs where the CUDA
  * allocator must not be called, a foreign-language host (cgo, JNI, a plugin) that owns only its
  * input and output buffers, a process whose pool already holds all device memory.  The logits
- * scratch is an 8 MiB array built into the library image (each GPU that loads the library keeps it
+ * scratch is a 10 MiB array built into the library image (each GPU that loads the library keeps it
  * until the process exits); the call itself performs no cudaMalloc / cudaFree and calls no
  * allocating routine.  The caller still passes inputs and outputs.
- *   - Limit: mq_router_workspace_bytes(T, H, E) <= 8 MiB (with 128 experts: any batch up to
- *     16384 tokens); larger requests return MQ_ERR_STATIC_SCRATCH_EXCEEDED, nothing launched.
+ *   - Limit: mq_router_workspace_bytes(T, H, E) <= 10 MiB; larger requests return
+ *     MQ_ERR_STATIC_SCRATCH_EXCEEDED, nothing launched.  The request is slices * T * E * 4 bytes and
+ *     the slice count falls as T grows, so it is not monotonic in T: with 128 experts and H = 2048 it
+ *     peaks at 9.22 MiB (T = 9440, two slices) and is 8 MiB at T = 16384, so every batch up to 16384
+ *     tokens fits (the largest that does is 20480 tokens).
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *     that device current).  Make that first call before starting any stream capture.
  *   - All calls on a device share the one array and it keeps the last call's contents.  Nothing in
@@ -171,6 +174,21 @@ int mq_grouped_swiglu_gather(const void* x, const int32_t* perm, const void* w_g
                              void* h, int32_t* d_status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Load-time stacking of per-expert tensors.  The reference's loaders leave one module per expert and
+ * projection (mini_qwen/model/loader.py:63-75 for dense checkpoints, :245-250 for GPTQ ones: 18 624
+ * tensors), and its block walks them in a Python loop; the grouped kernels index expert-major stacks.
+ * mq_stack_tensors builds one on the device for a host that has no tensor library:
+ *   out = concatenation of the n tensors of bytes_each bytes whose device addresses are in the DEVICE
+ *   array d_src_ptrs.  Dense experts: one call for the down weights [H,I] (n = E) and one for the gate
+ *   and up weights with the addresses in the order gate[0], up[0], gate[1], up[1], ... (n = 2E), which
+ *   gives w_gate_up [E, 2I, H]; W4A16 experts: one call per projection and buffer (qweight, scales,
+ *   qzeros).  sources_aligned16 != 0 promises that every source address is 16-byte aligned (16-byte
+ *   copies are then used when bytes_each % 16 == 0); n <= 65535.
+ */
+int mq_stack_tensors(const uint64_t* d_src_ptrs, int64_t n, int64_t bytes_each, int sources_aligned16,
+                     void* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * W4A16 linear.  Replaces w4a16_gemm (mini_qwen/kernels/w4a16_gemm.py:8-15,194-247) and,
  * with E > 1, the per-expert calls LinearW4A16.forward makes from the expert loop
  * (mini_qwen/model/layers/linear_w4a16.py:31-36):
@@ -225,14 +243,18 @@ int mq_w4a16_tc_swiglu(const void* xp, const float* xs,
  * expert-output buffer of cap_rows rows that its peers can address (peer_*_ptrs: device array of
  * G base addresses, entry r being the local buffer).  The slots a rank receives are ordered by
  * local expert and, inside an expert, by source rank (each source's slots in its own sorted order):
- * E/G ordinary groups for the grouped kernels.  None of these kernels waits on another GPU; the
- * caller orders the ranks between the calls (mq_ep_barrier or any stream-ordered collective).
+ * E/G ordinary groups for the grouped kernels.  The data kernels wait on nobody; the caller orders the
+ * ranks between them with mq_ep_barrier (or any stream-ordered collective).  mq_ep_barrier and
+ * mq_ep_exchange_plan DO wait on the other ranks, on the device, with a bounded poll: the ranks of a
+ * group must enter a layer call within the poll budget of one another (max_polls polls; 0 = the
+ * default of 2^22, one to two seconds), and a caller must read d_status before trusting an output.
  *
  * mq_ep_share_counts: writes this rank's per-expert counts (from its offsets [E+1]) into row `rank`
  *   of every peer's counts table int32 [G,E] (peer_counts_ptrs: G base addresses).
  * mq_ep_barrier: stream-ordered barrier across the G ranks through a signal array int32 [G] on every
- *   rank (peer_signal_ptrs) and a local epoch counter.  The wait is bounded (about a second); on
- *   expiry MQ_DEV_WAIT_EXPIRED is set in d_status and the kernel returns.
+ *   rank (peer_signal_ptrs) and a local epoch counter.  The wait is bounded (max_polls polls of every
+ *   peer's slot, 0 = default, at most 2^22); on expiry MQ_DEV_WAIT_EXPIRED is set in d_status and the
+ *   kernel returns; the stream and the context stay usable.
  * mq_ep_plan: all_counts int32 [G,E] (per-expert slot counts of every rank) ->
  *   send_base int32 [E]: slot in the owner's receive order where this rank's slots of expert e start;
  *   seg_offsets int32 [E/G+1]: prefix sums of this rank's receive groups (one per local expert).
@@ -249,15 +271,18 @@ int mq_w4a16_tc_swiglu(const void* xp, const float* xs,
 int mq_ep_share_counts(const int32_t* offsets, int64_t E, int64_t G, int64_t rank,
                        const uint64_t* peer_counts_ptrs, void* stream);
 int mq_ep_barrier(const uint64_t* peer_signal_ptrs, int32_t* epoch_counter, int64_t G, int64_t rank,
-                  int32_t* d_status, void* stream);
+                  int64_t max_polls, int32_t* d_status, void* stream);
 int mq_ep_plan(const int32_t* all_counts, int64_t G, int64_t rank, int64_t E,
                int32_t* send_base, int32_t* seg_offsets, void* stream);
 /* mq_ep_share_counts, mq_ep_barrier and mq_ep_plan in one launch (the plan is formed from this rank's
- * own counts table, peer_counts_ptrs[rank], once every rank has written its row). */
+ * own counts table, peer_counts_ptrs[rank], once every rank has written its row).  When the wait runs
+ * out, the plan written is one that moves nothing: send_base[e] = 0x3FFFFFFF for every expert (the
+ * dispatch kernels drop rows outside [0, cap_rows) and set MQ_DEV_EP_OVERFLOW) and seg_offsets all 0
+ * (the grouped kernels get no rows), so nothing is computed from an incomplete counts table. */
 int mq_ep_exchange_plan(const int32_t* offsets, int64_t E, int64_t G, int64_t rank,
                         const uint64_t* peer_counts_ptrs, const uint64_t* peer_signal_ptrs,
                         int32_t* epoch_counter, int32_t* send_base, int32_t* seg_offsets,
-                        int32_t* d_status, void* stream);
+                        int64_t max_polls, int32_t* d_status, void* stream);
 int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, const int32_t* offsets,
                    const int32_t* send_base, int64_t S, int64_t K, int64_t H, int64_t E, int64_t G,
                    int64_t rank, const uint64_t* peer_recv_ptrs, const uint64_t* peer_home_ptrs,

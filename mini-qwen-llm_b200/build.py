@@ -46,6 +46,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
+    extra += os.environ.get("MQMOE_NVCC_FLAGS", "").split()      # e.g. -DNAME=value for a kernel experiment
 
     def compile_one(src: Path):
         obj = OBJ_DIR / (src.stem + ".o")

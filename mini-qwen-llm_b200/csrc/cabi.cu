@@ -29,7 +29,7 @@ extern "C" const char* mq_status_string(int status) {
     case MQ_ERR_LAUNCH_FAILED: return "kernel launch failed";
     case MQ_ERR_DRIVER_ENTRY: return "cuTensorMapEncodeTiled unavailable or failed";
     case MQ_ERR_STATIC_SCRATCH_EXCEEDED:
-      return "request needs more scratch than the 8 MiB array built into the library (use the entry point "
+      return "request needs more scratch than the 10 MiB array built into the library (use the entry point "
              "that takes a caller workspace)";
     default: return "unknown status";
   }

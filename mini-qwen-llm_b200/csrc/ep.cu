@@ -5,8 +5,13 @@
 // then moving them with a collective, the dispatch kernel gathers each token row straight into the
 // receive buffer of the GPU that owns its expert (16-byte peer stores over NVLink), and the combine
 // kernel reads each expert output row straight from the GPU that produced it (16-byte peer loads)
-// while forming the weighted sum.  No kernel here waits on another GPU: ordering between the ranks
-// is a stream-ordered collective issued by the host side between the kernels.
+// while forming the weighted sum.  Ordering between the ranks is a flag barrier on the stream
+// (ep_barrier_kernel, and the same code inside ep_exchange_plan_kernel): a rank writes its epoch into
+// every peer's signal array and polls its own array until every peer's epoch has arrived.  The poll is
+// bounded (EP_SPIN_LIMIT polls by default, one to two seconds); when it runs out the kernel sets
+// MQ_DEV_WAIT_EXPIRED, leaves a plan that sends and computes nothing, and returns.  The ranks of a group
+// must therefore enter a layer call within that time of one another, and the caller has to read the
+// status word before it trusts an output.  The data kernels (dispatch, combine) wait on nobody.
 //
 // Receive layout on every rank: slots grouped by local expert and, inside an expert, by source rank
 // (each source's slots in its own expert-sorted order).  The grouped GEMM kernels see E_local ordinary
@@ -64,10 +69,11 @@ ep_share_counts_kernel(const int32_t* __restrict__ offsets, int E, int G, int ra
 // The wait is bounded; when it runs out the kernel records MQ_DEV_WAIT_EXPIRED and returns, so a
 // missing rank costs a second, not a hang.
 constexpr uint32_t EP_SPIN_LIMIT = 1u << 22;
+constexpr int EP_DROP_BASE = 0x3FFFFFFF;         // send_base of a plan that must not send: beyond every buffer
 
 __global__ void __launch_bounds__(32)
 ep_barrier_kernel(const uint64_t* __restrict__ peer_sig, int32_t* __restrict__ epoch_ctr, int G, int rank,
-                  int32_t* __restrict__ status) {
+                  uint32_t max_polls, int32_t* __restrict__ status) {
   __shared__ int s_epoch;
   if (threadIdx.x == 0) {
     s_epoch = *epoch_ctr + 1;
@@ -86,7 +92,7 @@ ep_barrier_kernel(const uint64_t* __restrict__ peer_sig, int32_t* __restrict__ e
     int v;
     do {
       asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine + r) : "memory");
-    } while (v < epoch && ++spin < EP_SPIN_LIMIT);
+    } while (v < epoch && ++spin < max_polls);
     if (v < epoch) atomicOr(status, (int)MQ_DEV_WAIT_EXPIRED);
   }
 }
@@ -97,9 +103,11 @@ __global__ void __launch_bounds__(256)
 ep_exchange_plan_kernel(const int32_t* __restrict__ offsets, int E, int G, int rank,
                         const uint64_t* __restrict__ peer_counts, const uint64_t* __restrict__ peer_sig,
                         int32_t* __restrict__ epoch_ctr, int32_t* __restrict__ send_base,
-                        int32_t* __restrict__ seg_offsets, int32_t* __restrict__ status) {
+                        int32_t* __restrict__ seg_offsets, uint32_t max_polls, int32_t* __restrict__ status) {
   __shared__ int s_epoch;
+  __shared__ int s_expired;
   __shared__ int s_tot[1024];                    // slots per expert over all sources
+  if (threadIdx.x == 0) s_expired = 0;
   const int el = E / G;
   for (int i = threadIdx.x; i < E * G; i += blockDim.x) {
     const int d = i / E, e = i - d * E;
@@ -125,11 +133,22 @@ ep_exchange_plan_kernel(const int32_t* __restrict__ offsets, int E, int G, int r
       int v;
       do {
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine + r) : "memory");
-      } while (v < epoch && ++spin < EP_SPIN_LIMIT);
-      if (v < epoch) atomicOr(status, (int)MQ_DEV_WAIT_EXPIRED);
+      } while (v < epoch && ++spin < max_polls);
+      if (v < epoch) {
+        atomicOr(status, (int)MQ_DEV_WAIT_EXPIRED);
+        s_expired = 1;
+      }
     }
   }
   __syncthreads();
+  if (s_expired) {
+    // A rank did not arrive: its row of the counts table is stale or was never written.  Leave a plan that
+    // sends nothing (every slot's row number lies beyond any receive buffer, so the dispatch kernels drop
+    // it) and gives the grouped kernels no rows, instead of one built from those counts.
+    for (int e = threadIdx.x; e < E; e += blockDim.x) send_base[e] = EP_DROP_BASE;
+    for (int j = threadIdx.x; j <= el; j += blockDim.x) seg_offsets[j] = 0;
+    return;
+  }
   const int32_t* all_counts = reinterpret_cast<const int32_t*>(peer_counts[rank]);   // [G, E], written by the peers
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int tot = 0;
@@ -170,7 +189,7 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm
   const int e = lo;
   const int d = e / el;
   const int64_t row = (int64_t)send_base[e] + (p - offsets[e]);
-  if (row >= cap_rows) {                    // receive buffer too small for this routing: flag, do not write
+  if (row < 0 || row >= cap_rows) {         // outside the receive buffer (too small, or a plan that sends nothing)
     if (lane == 0) { atomicOr(status, 2); slot_dst[p] = -1; }
     return;
   }
@@ -342,7 +361,7 @@ ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict
   }
   const int e = lo, d = e / el;
   const int64_t row = (int64_t)send_base[e] + (p - offsets[e]);
-  if (row >= cap_rows) {                    // slot table of the owner too small for this routing
+  if (row < 0 || row >= cap_rows) {         // outside the owner's slot table (too small, or a plan that sends nothing)
     atomicOr(status, 2);
     slot_dst[p] = -1;
     return;
@@ -435,11 +454,12 @@ extern "C" int mq_ep_share_counts(const int32_t* offsets, int64_t E, int64_t G, 
 }
 
 extern "C" int mq_ep_barrier(const uint64_t* peer_signal_ptrs, int32_t* epoch_counter, int64_t G, int64_t rank,
-                             int32_t* d_status, void* stream) {
+                             int64_t max_polls, int32_t* d_status, void* stream) {
   using namespace mq;
   if (G <= 0 || rank < 0 || rank >= G || !peer_signal_ptrs || !epoch_counter || !d_status) return MQ_ERR_INVALID_ARGUMENT;
-  ep_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(peer_signal_ptrs, epoch_counter, (int)G,
-                                                                          (int)rank, d_status);
+  if (max_polls < 0 || max_polls > (int64_t)EP_SPIN_LIMIT) return MQ_ERR_INVALID_ARGUMENT;
+  ep_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      peer_signal_ptrs, epoch_counter, (int)G, (int)rank, max_polls ? (uint32_t)max_polls : EP_SPIN_LIMIT, d_status);
   return check_launch();
 }
 
@@ -521,14 +541,15 @@ extern "C" int mq_ep_dispatch_unique(const void* x, int dtype, const int32_t* un
 extern "C" int mq_ep_exchange_plan(const int32_t* offsets, int64_t E, int64_t G, int64_t rank,
                                    const uint64_t* peer_counts_ptrs, const uint64_t* peer_signal_ptrs,
                                    int32_t* epoch_counter, int32_t* send_base, int32_t* seg_offsets,
-                                   int32_t* d_status, void* stream) {
+                                   int64_t max_polls, int32_t* d_status, void* stream) {
   using namespace mq;
   if (E <= 0 || G <= 0 || rank < 0 || rank >= G || E % G != 0) return MQ_ERR_INVALID_ARGUMENT;
+  if (max_polls < 0 || max_polls > (int64_t)EP_SPIN_LIMIT) return MQ_ERR_INVALID_ARGUMENT;
   if (E > 1024) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (!offsets || !peer_counts_ptrs || !peer_signal_ptrs || !epoch_counter || !send_base || !seg_offsets || !d_status)
     return MQ_ERR_INVALID_ARGUMENT;
   ep_exchange_plan_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       offsets, (int)E, (int)G, (int)rank, peer_counts_ptrs, peer_signal_ptrs, epoch_counter, send_base, seg_offsets,
-      d_status);
+      max_polls ? (uint32_t)max_polls : EP_SPIN_LIMIT, d_status);
   return check_launch();
 }

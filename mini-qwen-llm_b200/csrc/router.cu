@@ -538,7 +538,10 @@ extern "C" int mq_router_topk(const void* x, int x_dtype, const void* w, int w_d
 // Host code must not pass the array's name to a kernel: on the host that name is only a stand-in
 // for the symbol, not a device address.  The address is looked up once per device with
 // cudaGetSymbolAddress while that device is current, and that pointer is what the kernels get.
-constexpr size_t R_STATIC_SCRATCH_BYTES = (size_t)8 << 20;   // 8 MiB: any batch up to 16384 tokens at 128 experts
+// 10 MiB.  The logits take slices * T * E * 4 bytes and the slice count falls as the batch grows; at 128
+// experts and 16-bit inputs the largest request up to 16384 tokens is 2 slices x 9440 tokens = 9.22 MiB
+// (one slice from 9441 tokens on: 8 MiB at 16384), so every batch up to 16384 tokens fits.
+constexpr size_t R_STATIC_SCRATCH_BYTES = (size_t)10 << 20;
 static __device__ __align__(256) float g_router_static_scratch[R_STATIC_SCRATCH_BYTES / sizeof(float)];
 
 namespace mq {

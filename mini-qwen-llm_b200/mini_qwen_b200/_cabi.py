@@ -34,15 +34,16 @@ PROTOTYPES = {
     "mq_grouped_swiglu": (c_int, [_P, _P, _P, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
     "mq_grouped_gemm_scatter": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _I, _P, _P]),
     "mq_grouped_swiglu_gather": (c_int, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
+    "mq_stack_tensors": (c_int, [_P, _L, _L, _I, _P, _P]),
     "mq_w4a16_grouped_gemm": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P]),
     "mq_w4a16_grouped_swiglu": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P]),
     "mq_w4a16_tc_prep": (c_int, [_P, _P, _L, _L, _L, _I, _P, _P, _P]),
     "mq_w4a16_tc_gemm": (c_int, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P]),
     "mq_w4a16_tc_swiglu": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P]),
     "mq_ep_share_counts": (c_int, [_P, _L, _L, _L, _P, _P]),
-    "mq_ep_barrier": (c_int, [_P, _P, _L, _L, _P, _P]),
+    "mq_ep_barrier": (c_int, [_P, _P, _L, _L, _L, _P, _P]),
     "mq_ep_plan": (c_int, [_P, _L, _L, _L, _P, _P, _P]),
-    "mq_ep_exchange_plan": (c_int, [_P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P]),
+    "mq_ep_exchange_plan": (c_int, [_P, _L, _L, _L, _P, _P, _P, _P, _P, _L, _P, _P]),
     "mq_ep_dispatch": (c_int, [_P, _I, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _L, _P, _P, _P]),
     "mq_ep_unique_rows": (c_int, [_P, _L, _L, _L, _L, _P, _P]),
     "mq_ep_dispatch_unique": (c_int, [_P, _I, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _P, _P, _P, _L, _P, _P, _P]),

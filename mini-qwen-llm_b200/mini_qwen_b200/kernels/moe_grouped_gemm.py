@@ -63,6 +63,7 @@ def moe_grouped_swiglu(permuted_hidden: torch.Tensor, gate_up_weights: torch.Ten
     groups = expert_offsets.numel() - 1
     assert I2 % 2 == 0 and permuted_hidden.shape[1] == H and groups >= E and groups % E == 0
     a = permuted_hidden.contiguous()
+    gate_up_weights = gate_up_weights.contiguous()
     S = a.shape[0]
     h = (torch.zeros if zero_init else torch.empty)(S, I2 // 2, dtype=a.dtype, device=a.device)
     if status is None:
@@ -92,6 +93,7 @@ def moe_grouped_swiglu_gather(hidden_states: torch.Tensor, perm: torch.Tensor, t
     _cabi.require_cuda(hidden_states, perm, gate_up_weights, expert_offsets)
     E, I2, H = gate_up_weights.shape
     x = hidden_states.contiguous()
+    gate_up_weights = gate_up_weights.contiguous()
     T = x.shape[0]
     S = perm.numel()
     assert x.shape[1] == H

@@ -19,8 +19,17 @@ from .. import _cabi
 _single_offsets: dict = {}   # (M, device) -> int32 [0, M]; a single linear is a one-expert group
 
 
+def _offsets32(expert_offsets: torch.Tensor) -> torch.Tensor:
+    """The kernels read int32 offsets; ``moe_permute`` returns int64 ones, as the reference does."""
+    assert expert_offsets.is_cuda, "w4a16 kernels run on CUDA tensors only"
+    off = expert_offsets if expert_offsets.dtype == torch.int32 else expert_offsets.to(torch.int32)
+    return off.contiguous()
+
+
 def _check_w4(x, qweight, scales, qzeros, group_size, E):
     assert x.is_cuda and qweight.is_cuda, "w4a16 kernels run on CUDA tensors only"
+    assert qweight.is_contiguous() and scales.is_contiguous() and qzeros.is_contiguous(), \
+        "qweight, scales and qzeros must be contiguous (the kernels index them as dense expert-major stacks)"
     assert x.dtype == torch.bfloat16, "activations must be bfloat16"
     assert qweight.dtype == torch.int32 and qzeros.dtype == torch.int32 and scales.dtype == torch.bfloat16
     K = x.shape[-1]
@@ -40,6 +49,7 @@ def w4a16_grouped_gemm(x, qweight, scales, qzeros, expert_offsets, group_size: i
     qweight [E, K/8, N], scales [E, K/g, N], qzeros [E, K/g, N/8], offsets int32 [E+1]."""
     E = qweight.shape[0]
     K, N = _check_w4(x, qweight, scales, qzeros, group_size, E)
+    expert_offsets = _offsets32(expert_offsets)
     groups = expert_offsets.numel() - 1       # E, or G * E (group g -> weight set g % E)
     assert groups >= E and groups % E == 0
     x = x.contiguous()
@@ -60,6 +70,7 @@ def w4a16_grouped_swiglu(x, gate, up, expert_offsets, group_size: int = 128, zer
     E = gate[0].shape[0]
     K, N = _check_w4(x, *gate, group_size, E)
     _check_w4(x, *up, group_size, E)
+    expert_offsets = _offsets32(expert_offsets)
     groups = expert_offsets.numel() - 1
     assert groups >= E and groups % E == 0
     x = x.contiguous()
@@ -125,6 +136,7 @@ def w4a16_tc_swiglu(xp, xs, gate, up, expert_offsets, group_size: int = 128, sta
     E = gate[0].shape[0]
     K, N = _check_w4(xp, *gate, group_size, E)
     _check_w4(xp, *up, group_size, E)
+    expert_offsets = _offsets32(expert_offsets)
     groups = expert_offsets.numel() - 1
     S = xp.shape[0]
     h = torch.empty(S, N, dtype=torch.bfloat16, device=xp.device)
@@ -143,6 +155,7 @@ def w4a16_tc_gemm(xp, xs, qweight, scales, qzeros, expert_offsets, group_size: i
     """One W4A16 projection per group on prepared activations; natural column order."""
     E = qweight.shape[0]
     K, N = _check_w4(xp, qweight, scales, qzeros, group_size, E)
+    expert_offsets = _offsets32(expert_offsets)
     groups = expert_offsets.numel() - 1
     S = xp.shape[0]
     if out is None:

@@ -98,10 +98,18 @@ class PeerExchange:
     Ordering between ranks is three stream-ordered barriers per layer call: after the counts have
     been shared, after the dispatch kernels and after the down projection.  The barrier is a
     one-warp kernel that writes an epoch into every peer's signal array and polls its own, with a
-    bounded number of polls (an expired wait sets a status bit; it never hangs).
+    bounded number of polls (an expired wait sets a status bit; it never hangs).  The ranks must
+    therefore enter a layer call within the poll budget of one another (one to two seconds), and
+    ``check_status()`` has to be called after a step before its output is trusted: an expired barrier
+    leaves a plan that moves and computes nothing, so the output of that call is meaningless.
     """
 
     def __init__(self, group, device, cap_rows: int, hidden: int, dtype: torch.dtype):
+        import os
+
+        # every byte moves in this library's kernels with plain peer loads and stores: the buffers need no
+        # NVLink multicast binding (a rank that dies while bound to one disturbs its peers' GPUs)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import _cabi
@@ -110,6 +118,7 @@ class PeerExchange:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.cap_rows, self.hidden, self.dtype = cap_rows, hidden, dtype
+        self.max_polls = 0             # poll budget of the rank barriers (0 = the library's default, 1-2 s)
         if self.world * cap_rows >= 2 ** 31:
             raise ValueError("expert-parallel buffer too large for 32-bit slot addresses")
         self.recv = symm_mem.empty(cap_rows * hidden, dtype=dtype, device=device)
@@ -143,7 +152,7 @@ class PeerExchange:
         kernels launched before it have finished."""
         c = self._cabi
         dev = self.status.device
-        rc = c.load().mq_ep_barrier(c.ptr(self.sig_ptrs), c.ptr(self._epoch), self.world, self.rank,
+        rc = c.load().mq_ep_barrier(c.ptr(self.sig_ptrs), c.ptr(self._epoch), self.world, self.rank, self.max_polls,
                                     c.ptr(self.status), c.stream_ptr(dev))
         c.check(rc, "mq_ep_barrier")
         c.count_launches(1)
@@ -164,9 +173,12 @@ class PeerExchange:
     def _counts_table(self, E: int, dev) -> None:
         if self._counts is None or self._counts.numel() != self.world * E:
             self._counts = self._symm.empty(self.world * E, dtype=torch.int32, device=dev)
+            self._counts.zero_()       # a row a late rank never writes then reads as "no slots", not as garbage
             h = self._symm.rendezvous(self._counts, self.group)
             self._handles += (h,)
             self.counts_ptrs = torch.tensor(list(h.buffer_ptrs), dtype=torch.int64, device=dev)
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=self.group)   # every rank's table is zeroed before anyone writes into it
 
     def exchange_plan(self, off32: torch.Tensor):
         """``share_counts``, ``rank_barrier`` and ``plan`` in one launch: (send_base, seg_offsets)."""
@@ -178,7 +190,7 @@ class PeerExchange:
         c = self._cabi
         rc = c.load().mq_ep_exchange_plan(c.ptr(off32), E, self.world, self.rank, c.ptr(self.counts_ptrs),
                                           c.ptr(self.sig_ptrs), c.ptr(self._epoch), c.ptr(send_base), c.ptr(seg),
-                                          c.ptr(self.status), c.stream_ptr(dev))
+                                          self.max_polls, c.ptr(self.status), c.stream_ptr(dev))
         c.check(rc, "mq_ep_exchange_plan")
         c.count_launches(1)
         return send_base, seg

@@ -1,5 +1,8 @@
 """Expert parallelism on 2+ GPUs: one process per GPU over NCCL; every rank's output must match the
-single-process CPU oracle on the concatenated batch, with routing bit-exact.  Skipped with one GPU."""
+single-process CPU oracle on the concatenated batch, with routing bit-exact.  Skipped with one GPU.
+
+Verdicts are collective: after every check the ranks agree (an all-reduce of an ok flag) on whether to
+go on, so no rank leaves while its peers are still issuing kernels that store into its buffers."""
 import os
 import socket
 
@@ -10,6 +13,14 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 
+RTOL, ATOL = 2e-2, 2e-3
+SHAPES = {
+    # name: (tokens per rank, H, E, K, I, router-bias strength)
+    "small": (300, 512, 16, 4, 256, 2.0),
+    # the benchmark layer: 128 experts, top-8, H=2048, I=768 (16 experts per rank on 8 GPUs)
+    "layer": (512, 2048, 128, 8, 768, 1.0),
+}
+
 
 def _free_port():
     with socket.socket() as s:
@@ -17,35 +28,53 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, w4, mode):
+class _Agree:
+    """Turns per-rank checks into one verdict for the whole group."""
+
+    def __init__(self, dev):
+        self.dev = dev
+        self.failures = []
+
+    def check(self, ok: bool, what: str) -> bool:
+        if not ok:
+            self.failures.append(what)
+        flag = torch.tensor([1 if ok else 0], device=self.dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return bool(flag.item())
+
+
+def _worker(rank, world, port, w4, mode, shape):
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     for p in (root, os.path.join(root, "mini-qwen-llm_b200")):
         if p not in sys.path:
             sys.path.insert(0, p)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"      # the library only uses plain peer loads and stores
     from mini_qwen_b200 import Qwen3MoEConfig, synthetic
     from mini_qwen_b200.kernels import moe_router
     from mini_qwen_b200.model.layers import LinearW4A16, Qwen3MoEBlock
     from oracle import moe_oracle as O
 
-    os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
                             device_id=dev)
+    agree = _Agree(dev)
     try:
-        T_local, H, E, K, I = 300, 512, 16, 4, 256
+        T_local, H, E, K, I, strength = SHAPES[shape]
         el = E // world
         lo, hi = rank * el, (rank + 1) * el
         cfg = Qwen3MoEConfig(hidden_size=H, intermediate_size=I, num_experts=E, num_experts_per_tok=K)
-        bias = synthetic.zipf_router_bias(3, E, strength=2.0)
+        bias = synthetic.zipf_router_bias(3, E, strength=strength)
+        torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
         if not w4:
             lay = synthetic.dense_layer(21, T_local * world, H, E, K, I, torch.bfloat16)
             w13 = torch.cat([lay.gate[lo:hi], lay.up[lo:hi]], dim=1).to(dev)
             blk = Qwen3MoEBlock.from_stacked(cfg, lay.router.to(dev), w13, lay.down[lo:hi].to(dev),
                                              ep_group=dist.group.WORLD, ep_mode=mode)
-            ref, ref_ids, _, _ = O.block_forward(lay.x, lay.router, lay.gate, lay.up, lay.down, K, True, bias)
             router_w = lay.router
+            expert_fn = None
         else:
             lay = synthetic.w4a16_layer(22, T_local * world, H, E, K, I, group=128)
             blk = Qwen3MoEBlock(cfg, ep_group=dist.group.WORLD, ep_mode=mode)
@@ -57,45 +86,84 @@ def _worker(rank, world, port, w4, mode):
             blk.gate.weight.data = router_w
             blk = blk.to(dev)
 
-            def fn(e, x_e):
+            def expert_fn(e, x_e):
                 trios = [O.gptq_buffers(p.qweight[e], p.qzeros[e], p.scales[e]) for p in (lay.gate, lay.up, lay.down)]
                 return O.w4a16_expert(x_e, *trios, 128)
-            ref, ref_ids, _, _ = O.block_forward(lay.x, router_w, None, None, None, K, True, bias, expert_fn=fn)
+        # every rank checks its own slice: the oracle routes and evaluates these rows only (an expert's output
+        # for a row does not depend on the other rows)
+        sl = slice(rank * T_local, (rank + 1) * T_local)
+        if w4:
+            ref, ref_ids, _, _ = O.block_forward(lay.x[sl], router_w, None, None, None, K, True, bias, expert_fn=expert_fn)
+        else:
+            ref, ref_ids, _, _ = O.block_forward(lay.x[sl], lay.router, lay.gate, lay.up, lay.down, K, True, bias)
         blk.router_bias = bias.to(dev)
-        x = lay.x[rank * T_local:(rank + 1) * T_local].to(dev)
+        x = lay.x[sl].to(dev)
         out = blk(x)
         ids, _ = moe_router(x, router_w.to(dev), K, bias=bias.to(dev))
-        assert torch.equal(ids.cpu(), ref_ids[rank * T_local:(rank + 1) * T_local])
-        want = ref[rank * T_local:(rank + 1) * T_local].float()
-        got = out.cpu().float()
+        go = agree.check(torch.equal(ids.cpu(), ref_ids), f"rank {rank}: expert ids differ from the oracle")
+        want, got = ref.float(), out.cpu().float()
         err = (got - want).abs()
-        ok = err <= 2e-3 * max(1.0, want.abs().max().item()) + 2e-2 * want.abs()
-        assert bool(ok.all()), f"rank {rank}: max err {err.max().item()}"
-        assert torch.equal(blk(x), out)                      # deterministic across calls
-        if mode == "p2p":
-            blk._peer.check_status()                          # no receive-buffer overflow
+        if w4:
+            # the quantised layer's outputs reach magnitude 10-100 from bf16 intermediates: same bar as the
+            # single-GPU block test (share of elements outside the literal bar, bounded; the rest close)
+            outside = (err > ATOL + RTOL * want.abs()).float().mean().item()
+            ok = outside <= 5e-3 and (err - RTOL * want.abs()).max().item() <= ATOL * max(1.0, want.abs().max().item())
+            msg = f"rank {rank}: {outside:.4%} of the elements outside rtol/atol, max err {err.max().item():.4g}"
+        else:
+            ok = bool((err <= ATOL + RTOL * want.abs()).all())
+            msg = f"rank {rank}: max err {err.max().item():.4g} beyond rtol {RTOL} / atol {ATOL}"
+        go = agree.check(ok, msg) and go
+        if go:
+            go = agree.check(torch.equal(blk(x), out), f"rank {rank}: not deterministic across calls")
+        if go and mode == "p2p":
+            status_ok = True
+            try:
+                blk.check_status()                            # no expired barrier, no receive-buffer overflow
+            except RuntimeError as exc:
+                status_ok = False
+                agree.failures.append(str(exc))
+            go = agree.check(status_ok, f"rank {rank}: device status")
             # return by the down projection's own stores or by the combine's loads, dispatch per slot or per
             # (token, rank): all four give the same bits
             for ret, disp in (("pull", "unique"), ("pull", "slots"), ("fused", "slots"), ("fused", "unique")):
+                if not go:
+                    break
                 blk.ep_return, blk.ep_dispatch = ret, disp
-                assert torch.equal(blk(x), out), (ret, disp)
-            blk.check_status()
-            from mini_qwen_b200.graph import CapturedForward
-            cap = CapturedForward(blk, x)                     # collective: every rank captures and replays
-            assert torch.equal(cap.replay(), out)
-            assert torch.equal(cap.replay(), out)
-            blk.check_status()
-            out_small = blk(x[:17])                          # fewer tokens than the buffers were sized for
-            assert out_small.shape == (17, H)
+                go = agree.check(torch.equal(blk(x), out), f"rank {rank}: {ret}/{disp} differs")
+            if go:
+                from mini_qwen_b200.graph import CapturedForward
+                cap = CapturedForward(blk, x)                 # collective: every rank captures and replays
+                same = torch.equal(cap.replay(), out) and torch.equal(cap.replay(), out)
+                go = agree.check(same, f"rank {rank}: graph replay differs")
+            if go:
+                out_small = blk(x[:17])                       # fewer tokens than the buffers were sized for
+                go = agree.check(tuple(out_small.shape) == (17, H), f"rank {rank}: short batch shape")
+        torch.cuda.synchronize()
+        dist.barrier()                                        # nobody leaves while kernels are in flight anywhere
     finally:
         dist.destroy_process_group()
+    assert not agree.failures, "; ".join(agree.failures)
+    assert go, "another rank failed (see its message)"
+
+
+def _world():
+    n = torch.cuda.device_count()
+    return 8 if n >= 8 else 4 if n >= 4 else 2 if n >= 2 else 1
 
 
 @pytest.mark.parametrize("mode", ["p2p", "nccl"])
 @pytest.mark.parametrize("w4", [False, True])
 def test_expert_parallel_block_matches_oracle(w4, mode):
-    world = torch.cuda.device_count()
+    world = _world()
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
-    world = 2 if world < 4 else 4
-    mp.spawn(_worker, args=(world, _free_port(), w4, mode), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), w4, mode, "small"), nprocs=world, join=True)
+
+
+def test_expert_parallel_layer_shape_on_all_gpus():
+    """The benchmark layer (bf16, 128 experts, top-8, H=2048, I=768) over every GPU of the box: with 8 GPUs
+    this is the 16-experts-per-rank path the scaling benchmark times."""
+    world = _world()
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mp.spawn(_worker, args=(world, _free_port(), False, "p2p", "layer"), nprocs=world, join=True)

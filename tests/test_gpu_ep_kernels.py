@@ -116,7 +116,81 @@ def test_exchange_plan_single_rank_matches_plan():
     counts_ptrs, sig_ptrs = _ptrs([counts]), _ptrs([sig])  # kept alive: the launches read them asynchronously
     for _ in range(2):                                    # the epoch advances; a second call must pass as well
         c.check(lib.mq_ep_exchange_plan(c.ptr(off32), E, 1, 0, c.ptr(counts_ptrs), c.ptr(sig_ptrs),
-                                        c.ptr(epoch), c.ptr(sb), c.ptr(seg), c.ptr(status), st), "exchange_plan")
+                                        c.ptr(epoch), c.ptr(sb), c.ptr(seg), 0, c.ptr(status), st), "exchange_plan")
     assert status.item() == 0 and epoch.item() == 2
     assert torch.equal(counts, off32[1:] - off32[:-1])
     assert torch.equal(seg, off32) and torch.equal(sb, off32[:-1])
+
+
+def test_bounded_waits_run_out_and_leave_a_plan_that_moves_nothing():
+    """The rank barrier's wait is bounded.  Two "ranks" are emulated with two signal arrays and two counts
+    tables on one device; rank 1 never launches anything, so rank 0's poll of its slot cannot succeed.
+    With a budget of 1024 polls the kernels return, MQ_DEV_WAIT_EXPIRED is set, the plan written is the
+    one that sends and computes nothing, a dispatch driven by that plan writes no row, the stream stays
+    usable, and once rank 1 does signal, the same barrier passes."""
+    c = _cabi
+    lib = c.load()
+    st = c.stream_ptr(DEV)
+    E, T, K, H, G = 8, 40, 2, 64, 2
+    g = torch.Generator().manual_seed(11)
+    ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    perm, inv, off32, _ = moe_permute_plan(ids, E, want_int64_offsets=False)
+    counts = [torch.full((G * E,), 12345, dtype=torch.int32, device=DEV) for _ in range(G)]   # stale garbage
+    sig = [torch.zeros(32, dtype=torch.int32, device=DEV) for _ in range(G)]
+    counts_ptrs, sig_ptrs = _ptrs(counts), _ptrs(sig)
+    epoch = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    sb = torch.full((E,), -5, dtype=torch.int32, device=DEV)
+    seg = torch.full((E // G + 1,), -5, dtype=torch.int32, device=DEV)
+
+    # 1. plain barrier: rank 1's slot of rank 0's array stays 0 < epoch 1
+    c.check(lib.mq_ep_barrier(c.ptr(sig_ptrs), c.ptr(epoch), G, 0, 1024, c.ptr(status), st), "barrier")
+    torch.cuda.synchronize()
+    assert status.item() & 1 and epoch.item() == 1
+    assert sig[1][0].item() == 1                      # rank 0 did signal its peer before it waited
+
+    # 2. fused counts + barrier + plan: expiry leaves the safe plan, not one built from the stale counts
+    status.zero_()
+    c.check(lib.mq_ep_exchange_plan(c.ptr(off32), E, G, 0, c.ptr(counts_ptrs), c.ptr(sig_ptrs), c.ptr(epoch),
+                                    c.ptr(sb), c.ptr(seg), 1024, c.ptr(status), st), "exchange_plan")
+    torch.cuda.synchronize()
+    assert status.item() & 1 and epoch.item() == 2
+    assert bool((sb == 0x3FFFFFFF).all()) and bool((seg == 0).all())
+
+    # 3. a dispatch on that plan drops every row (flags the overflow bit) and touches no buffer
+    cap = G * T * K
+    recv = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(G)]
+    home = [torch.full((cap,), -1, dtype=torch.int32, device=DEV) for _ in range(G)]
+    recv_ptrs, home_ptrs = _ptrs(recv), _ptrs(home)
+    slot_dst = torch.zeros(T * K, dtype=torch.int32, device=DEV)
+    c.check(lib.mq_ep_dispatch(c.ptr(x), c.dtype_code(x), c.ptr(perm), c.ptr(off32), c.ptr(sb), T * K, K, H, E, G, 0,
+                               c.ptr(recv_ptrs), c.ptr(home_ptrs), cap, c.ptr(slot_dst), c.ptr(status), st), "dispatch")
+    torch.cuda.synchronize()
+    assert status.item() & 2 and bool((slot_dst == -1).all())
+    assert all(not bool(r.any()) for r in recv) and all(bool((h == -1).all()) for h in home)
+
+    # 4. the stream still works, and with rank 1 present (its epoch written into rank 0's array, as its own
+    # barrier kernel would) the next barrier passes without touching the status word
+    status.zero_()
+    sig[0][1] = 3
+    c.check(lib.mq_ep_barrier(c.ptr(sig_ptrs), c.ptr(epoch), G, 0, 1024, c.ptr(status), st), "barrier")
+    torch.cuda.synchronize()
+    assert status.item() == 0 and epoch.item() == 3
+
+
+def test_stack_tensors_concatenates_device_tensors():
+    """mq_stack_tensors: the expert-major stack a host without a tensor library builds from per-expert tensors."""
+    c = _cabi
+    lib = c.load()
+    st = c.stream_ptr(DEV)
+    g = torch.Generator().manual_seed(3)
+    for shape, dtype in (((96, 64), torch.bfloat16), ((33, 5), torch.int32), ((7,), torch.uint8)):
+        parts = [torch.randint(0, 127, shape, generator=g).to(dtype).to(DEV) for _ in range(5)]
+        nbytes = parts[0].numel() * parts[0].element_size()
+        out = torch.empty((5,) + shape, dtype=dtype, device=DEV)
+        ptrs = _ptrs(parts)
+        aligned = int(all(p.data_ptr() % 16 == 0 for p in parts))
+        c.check(lib.mq_stack_tensors(c.ptr(ptrs), 5, nbytes, aligned, c.ptr(out), st), "stack")
+        torch.cuda.synchronize()
+        assert torch.equal(out, torch.stack(parts))

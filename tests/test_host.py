@@ -162,3 +162,25 @@ def test_from_stacked_shares_storage():
     assert blk.experts[2].up_proj.weight.data_ptr() == w13[2, 16:].data_ptr()
     assert torch.equal(blk.state_dict()["experts.3.down_proj.weight"], w2[3])
     assert blk._ready()["w13"].data_ptr() == w13.data_ptr()       # no restack needed
+
+
+def test_static_router_scratch_covers_every_batch_up_to_16384_tokens():
+    """mq_router_topk_static promises room for any batch up to 16384 tokens at the Qwen3-30B-A3B router
+    shape.  The request is not monotonic in T (the logits are kept in several K slices for small
+    batches), so every T is checked against the 10 MiB array, and the first refused batch size is pinned."""
+    lib = _cabi.load()
+    limit = 10 << 20
+    worst = max(lib.mq_router_workspace_bytes(T, 2048, 128) for T in range(1, 16385))
+    assert worst <= limit, worst
+    assert worst == 2 * 9440 * 128 * 4                  # the documented peak: two slices at 9440 tokens
+    assert lib.mq_router_workspace_bytes(20480, 2048, 128) == limit     # the largest batch that fits
+    # one token more is refused by the argument check, before anything touches a device
+    assert lib.mq_router_topk_static(None, 1, None, 1, None, 20481, 2048, 128, 8, 0, None, None, None, None) == 6
+
+
+def test_ep_entry_points_reject_bad_poll_budgets_without_a_gpu():
+    lib = _cabi.load()
+    assert lib.mq_ep_barrier(None, None, 2, 0, 0, None, None) == 1                  # null pointers
+    assert lib.mq_stack_tensors(None, 3, 64, 1, None, None) == 1                     # null pointers
+    assert lib.mq_stack_tensors(None, 0, 64, 1, None, None) == 0                     # nothing to do
+    assert lib.mq_stack_tensors(None, 70000, 64, 1, None, None) == 1

@@ -45,7 +45,10 @@ def test_static_router_matches_workspace_router_twice_in_a_row():
     g = torch.Generator().manual_seed(123)
     # first call: a prefill-sized batch (tiled kernel, several K slices); second: a decode batch (other
     # kernel, smaller footprint) that finds the first call's logits still in the array
-    shapes = [(4096, 2048, 128, 8, torch.bfloat16, True), (7, 2048, 128, 8, torch.bfloat16, False)]
+    # third: 9000 tokens, inside the range (8193..9440) where the logits are kept in two K slices and take
+    # more room than at 16384 tokens
+    shapes = [(4096, 2048, 128, 8, torch.bfloat16, True), (7, 2048, 128, 8, torch.bfloat16, False),
+              (9000, 2048, 128, 8, torch.bfloat16, True)]
     for T, H, E, K, dt, renorm in shapes:
         x = torch.randn(T, H, generator=g).to(dt).to(DEV)
         w = (torch.randn(E, H, generator=g) * 0.02).to(dt).to(DEV)
@@ -58,7 +61,7 @@ def test_static_router_matches_workspace_router_twice_in_a_row():
 
 def test_static_router_rejects_oversized_requests():
     lib = _cabi.load()
-    # 32768 tokens x 128 experts x 4 bytes is beyond the 8 MiB array: refused before any launch
+    # 32768 tokens x 128 experts x 4 bytes is beyond the 10 MiB array: refused before any launch
     rc = lib.mq_router_topk_static(None, 1, None, 1, None, 32768, 2048, 128, 8, 0, None, None, None, None)
     assert rc == 6
-    assert "8 MiB" in lib.mq_status_string(rc).decode()
+    assert "10 MiB" in lib.mq_status_string(rc).decode()
