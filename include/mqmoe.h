@@ -213,6 +213,28 @@ int mq_w4a16_grouped_swiglu(const void* x,
                             int64_t S, int64_t E, int64_t weight_period, int64_t I, int64_t H, int64_t group_size,
                             void* h, void* stream);
 
+/* The same two operations with PREPARED activations, the form the block's decode path uses (same results as
+ * the two calls above up to the order of the fp32 sums):
+ *   xp bf16 [S,Kd]: the expert-sorted rows; x_shuffled != 0: with the k order 0,4,1,5,2,6,3,7 inside every 8
+ *     (what mq_w4a16_tc_prep writes with shuffle = 1, and what mq_w4a16_stream_swiglu writes with
+ *     shuffle_out != 0), which saves the kernel four byte permutes per 32 k;
+ *   xs fp32 [S,32] or NULL: the rows' sums over every quantisation group (mq_w4a16_tc_prep); given, the
+ *     kernel skips the extra MMA pair per 32 k that otherwise forms them; requires x_shuffled;
+ *   shuffle_out != 0: h is written with its columns in the shuffled order, ready to be the xp of the down
+ *     projection (pass x_shuffled = 1 there).
+ * group_size == 128, N % 32 == 0, at most 384 row groups (MQ_ERR_UNSUPPORTED_SHAPE otherwise).  d_status
+ * (optional) receives MQ_DEV_WAIT_EXPIRED if a bounded wait on a bulk copy ran out. */
+int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shuffled,
+                           const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
+                           const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
+                           const int32_t* offsets, int64_t S, int64_t E, int64_t weight_period, int64_t I,
+                           int64_t H, int64_t group_size, int shuffle_out, void* h, int32_t* d_status,
+                           void* stream);
+int mq_w4a16_stream_gemm(const void* xp, const float* xs, int x_shuffled, const int32_t* qweight,
+                         const void* scales, const int32_t* qzeros, const int32_t* offsets, int64_t S,
+                         int64_t E, int64_t weight_period, int64_t N, int64_t Kd, int64_t group_size,
+                         void* out, int32_t* d_status, void* stream);
+
 /* The same two W4A16 operations on the tcgen05 tensor cores, for decode-size groups (any group size
  * is correct; it is tuned for groups of at most 32 rows).  The packed weights stream in by TMA in
  * the checkpoint layout, are turned into bf16 in registers and written to tensor memory, from where

@@ -8,9 +8,10 @@
 //   * A lane reads one 128-bit vector = 4 adjacent columns x 8 consecutive k of packed int4,
 //     straight in the checkpoint layout [K/8, N] (8 lanes cover a full 128-byte line).
 //   * Nibbles become bf16 with ONE logic op per pair: (w >> 4p) & 0x000F000F | 0x43004300 is the
-//     bf16 pair {128+q[p], 128+q[p+4]}.  The zero point is not subtracted per weight: with
+//     bf16 pair {128+q[p], 128+q[p+4]}, re-centred to {q[p]-8, q[p+4]-8} by one packed fma on the FMA
+//     pipe.  The zero point is not subtracted per weight: with
 //     xs = sum_k x[k] over the group (obtained from one extra MMA against a tile of ones),
-//        sum_k x[k] * (q[k] - z) = sum_k x[k] * (128 + q[k])  -  (128 + z) * xs ,
+//        sum_k x[k] * (q[k] - z) = sum_k x[k] * (q[k] - 8)  -  (z - 8) * xs ,
 //     and the right-hand side is evaluated once per group and column in fp32.
 //   * The biased integers are the A operand (16 columns x 16 k) of mma.sync.m16n8k16 with the
 //     activations as the 8-wide B operand ("swap-AB": rows of x are the narrow dimension); the k
@@ -50,11 +51,14 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   return r;
 }
 
-// pair p of word w -> bf16x2 {128 + q[p], 128 + q[p+4]}
+// pair p of word w -> bf16x2 {q[p] - 8, q[p+4] - 8}: the logic op makes {128 + q[p], 128 + q[p+4]}, a packed
+// fma on the (idle) FMA pipe takes the 136 off again, so that a group's sum stays as small as the result
+// instead of carrying 128 * sum(x) that has to cancel in fp32 later.
 __device__ __forceinline__ uint32_t biased_pair(uint32_t w, int p) {
-  uint32_t v;
+  uint32_t v, c;
   asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(w >> (4 * p)), "r"(0x000F000Fu), "r"(0x43004300u));
-  return v;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(c) : "r"(v), "r"(0x3F803F80u), "r"(0xC308C308u));
+  return c;
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -76,7 +80,7 @@ struct W4Stream {
   float master[2][4];
   float grp[2][4];
   float scale[4];
-  float zoff[4];            // 128 + zero point of the current group
+  float zoff[4];            // zero point of the current group, minus 8
 };
 
 __device__ __forceinline__ void stream_init(W4Stream& a) {
@@ -88,7 +92,7 @@ __device__ __forceinline__ void stream_init(W4Stream& a) {
   for (int c = 0; c < 4; ++c) { a.scale[c] = 0.0f; a.zoff[c] = 0.0f; }
 }
 
-// End of a group: master += s * (sum_k x*(128+q) - (128+z) * sum_k x), then restart the group sums.
+// End of a group: master += s * (sum_k x*(q-8) - (z-8) * sum_k x), then restart the group sums.
 __device__ __forceinline__ void stream_flush(W4Stream& a, const float (&xs)[4]) {
 #pragma unroll
   for (int m = 0; m < 2; ++m)
@@ -134,7 +138,7 @@ __device__ __forceinline__ void stream_set_group(W4Stream& a, const W4Meta& m) {
   a.scale[2] = __uint_as_float(m.s.y << 16);
   a.scale[3] = __uint_as_float(m.s.y & 0xffff0000u);
 #pragma unroll
-  for (int c = 0; c < 4; ++c) a.zoff[c] = (float)(128u + ((m.z >> (4 * c)) & 0xFu));
+  for (int c = 0; c < 4; ++c) a.zoff[c] = (float)((int)((m.z >> (4 * c)) & 0xFu) - 8);
 }
 
 // The y-th non-empty group of rows (y = blockIdx.y), found with ballots over the offsets; -1 if
@@ -366,8 +370,21 @@ void launch_w4_variant(const void* x, W4Proj p0, W4Proj p1, const int32_t* offse
       compact, reinterpret_cast<__nv_bfloat16*>(out));
 }
 
+}  // namespace
+
+// TMA-staged persistent stream kernel (w4a16_stream.cu): group size 128, N a multiple of 32.
+bool w4a16_stream_covers(int64_t S, int64_t E, int64_t period, int64_t N, int64_t Kd, int64_t group);
+int w4a16_stream(const void* x, const float* xs, bool x_shuffled, const int32_t* perm, int64_t top_k,
+                 const int32_t* qw0, const void* sc0, const int32_t* qz0, const int32_t* qw1, const void* sc1,
+                 const int32_t* qz1, bool swiglu, bool shuffle_out, const int32_t* offsets, int64_t S, int64_t E,
+                 int64_t period, int64_t N, int64_t Kd, void* out, int32_t* d_status, cudaStream_t st);
+
+namespace {
+
 int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* offsets, int64_t S, int64_t E,
-              int64_t period, int64_t N, int64_t Kd, int64_t group, void* out, cudaStream_t st) {
+              int64_t period, int64_t N, int64_t Kd, int64_t group, void* out, cudaStream_t st,
+              const int32_t* perm = nullptr, int64_t top_k = 1, int32_t* d_status = nullptr,
+              const float* xs = nullptr, bool x_shuffled = false, bool shuffle_out = false, bool want_stream = false) {
   if (S < 0 || E <= 0 || N <= 0 || Kd <= 0 || group <= 0) return MQ_ERR_INVALID_ARGUMENT;
   if (period <= 0 || period > E) return MQ_ERR_INVALID_ARGUMENT;
   if (group % 32 != 0 || Kd % group != 0 || N % 8 != 0 || E > 65535) return MQ_ERR_UNSUPPORTED_SHAPE;
@@ -376,6 +393,16 @@ int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* o
   if (swiglu && (!p1.qw || !p1.sc || !p1.qz)) return MQ_ERR_INVALID_ARGUMENT;
   if (!aligned16(x) || !aligned16(p0.qw) || !aligned16(p0.sc) || !aligned16(out)) return MQ_ERR_INVALID_ARGUMENT;
   if (swiglu && (!aligned16(p1.qw) || !aligned16(p1.sc))) return MQ_ERR_INVALID_ARGUMENT;
+  // Which kernel: the TMA-staged stream kernel is the faster one for the fused gate/up projection from a few
+  // dozen slots on (batch 64: 66 against 81 us; below 32 slots both are bound by launch latency), the per-lane
+  // cp.async kernel below for the single projection (40 against 43 us at batch 64: its K is short and it needs
+  // no K split).  The prepared-activation entry points ask for the stream kernel explicitly.
+  const bool stream = want_stream || (swiglu && S >= 32);
+  if (stream && w4a16_stream_covers(S, E, period, N, Kd, group))
+    return w4a16_stream(x, xs, x_shuffled, perm, top_k, p0.qw, p0.sc, p0.qz, p1.qw, p1.sc, p1.qz, swiglu, shuffle_out,
+                        offsets, S, E, period, N, Kd, out, d_status, st);
+  // the fallback kernel wants expert-sorted rows in natural order
+  if (perm != nullptr || x_shuffled || shuffle_out) return MQ_ERR_UNSUPPORTED_SHAPE;
   // few rows in total (a handful of experts hit): split K across the warps of a CTA to get enough CTAs;
   // otherwise every warp streams the whole K of its own column tile
   bool split = S <= 32;
@@ -411,4 +438,29 @@ extern "C" int mq_w4a16_grouped_swiglu(const void* x,
   mq::W4Proj pu{qweight_up, reinterpret_cast<const __nv_bfloat16*>(scales_up), qzeros_up};
   return mq::launch_w4(x, pg, pu, true, offsets, S, E, weight_period, I, H, group_size, h,
                        reinterpret_cast<cudaStream_t>(stream));
+}
+
+/* Prepared-activation forms: see include/mqmoe.h. */
+extern "C" int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shuffled,
+                                      const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
+                                      const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
+                                      const int32_t* offsets, int64_t S, int64_t E, int64_t weight_period, int64_t I,
+                                      int64_t H, int64_t group_size, int shuffle_out, void* h, int32_t* d_status,
+                                      void* stream) {
+  mq::W4Proj pg{qweight_gate, reinterpret_cast<const __nv_bfloat16*>(scales_gate), qzeros_gate};
+  mq::W4Proj pu{qweight_up, reinterpret_cast<const __nv_bfloat16*>(scales_up), qzeros_up};
+  if (!mq::w4a16_stream_covers(S, E, weight_period, I, H, group_size)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  return mq::launch_w4(xp, pg, pu, true, offsets, S, E, weight_period, I, H, group_size, h,
+                       reinterpret_cast<cudaStream_t>(stream), nullptr, 1, d_status, xs, x_shuffled != 0,
+                       shuffle_out != 0, true);
+}
+
+extern "C" int mq_w4a16_stream_gemm(const void* xp, const float* xs, int x_shuffled, const int32_t* qweight,
+                                    const void* scales, const int32_t* qzeros, const int32_t* offsets, int64_t S,
+                                    int64_t E, int64_t weight_period, int64_t N, int64_t Kd, int64_t group_size,
+                                    void* out, int32_t* d_status, void* stream) {
+  mq::W4Proj p{qweight, reinterpret_cast<const __nv_bfloat16*>(scales), qzeros};
+  if (!mq::w4a16_stream_covers(S, E, weight_period, N, Kd, group_size)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  return mq::launch_w4(xp, p, p, false, offsets, S, E, weight_period, N, Kd, group_size, out,
+                       reinterpret_cast<cudaStream_t>(stream), nullptr, 1, d_status, xs, x_shuffled != 0, false, true);
 }

@@ -15,9 +15,10 @@
 //   * the pairs come out in k order 0,4,1,5,2,6,3,7 inside every 8; the activations are stored in the
 //     same order by the preparation kernel (and by the gate/up epilogue for the down projection), so
 //     both operands agree and no permute instruction is spent;
-//   * zero points and scales never touch the weights: the tensor core sums x*(128+q) over one
-//     quantisation group (128 k) into a TMEM accumulator, four fold warps read it and add
-//     s * (D - (128+z) * xs) in fp32, xs = sum of x over the group (computed by the preparation kernel).
+//   * zero points and scales never touch the weights: the pairs are re-centred to q-8 (one packed fma),
+//     the tensor core sums x*(q-8) over one quantisation group (128 k) into a TMEM accumulator, four
+//     fold warps read it and add s * (D - (z-8) * xs) in fp32, xs = sum of x over the group (computed
+//     by the preparation kernel).
 //     The dequantised weight is never rounded.
 // Every wait is a bounded mbarrier wait; on expiry the kernel sets MQ_DEV_WAIT_EXPIRED and leaves.
 //
@@ -346,7 +347,12 @@ w4a16_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
             for (int j = 0; j < 4; ++j)
 #pragma unroll
-              for (int p = 0; p < 4; ++p) r[4 * j + p] = ((w[4 * hh + j] >> (4 * p)) & 0x000F000Fu) | 0x43004300u;
+              for (int p = 0; p < 4; ++p) {
+                // {128+q_p, 128+q_(p+4)}, re-centred to {q_p - 8, q_(p+4) - 8} by a packed fma (FMA pipe), so
+                // that the group's sum in tensor memory stays as small as the result
+                const uint32_t biased = ((w[4 * hh + j] >> (4 * p)) & 0x000F000Fu) | 0x43004300u;
+                asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r[4 * j + p]) : "r"(biased), "r"(0x3F803F80u), "r"(0xC308C308u));
+              }
             w_tmem_st16(tmem_base + ((uint32_t)(quad * 32) << 16) + W_A_COL + b * 128 + sub * 64 + khalf * 32 + hh * 16, r);
           }
         }
@@ -387,13 +393,13 @@ w4a16_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
         for (int i = 0; i < W_TN; ++i) acc[s][i] = 0.0f;
       for (int g = 0; g < G && ok; ++g, ++gc) {
-        // this group's scale and (128 + zero point) for the lane's column, fetched before the wait
+        // this group's scale and (zero point - 8) for the lane's column, fetched before the wait
         float sc[NSUB], zb[NSUB];
         sc[0] = __bfloat162float(sc0[(size_t)g * N]);
-        zb[0] = 128.0f + (float)((qz0[(size_t)g * (N / 8)] >> zshift) & 15);
+        zb[0] = (float)((int)((qz0[(size_t)g * (N / 8)] >> zshift) & 15) - 8);
         if (SWIGLU) {
           sc[NSUB - 1] = __bfloat162float(sc1[(size_t)g * N]);
-          zb[NSUB - 1] = 128.0f + (float)((qz1[(size_t)g * (N / 8)] >> zshift) & 15);
+          zb[NSUB - 1] = (float)((int)((qz1[(size_t)g * (N / 8)] >> zshift) & 15) - 8);
         }
         const int b = gc & 1;
         ok = __all_sync(0xffffffffu, w_mbar_wait(done(b), (uint32_t)((gc >> 1) & 1), abort_flag, d_status));

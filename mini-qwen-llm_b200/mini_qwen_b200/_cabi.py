@@ -37,6 +37,8 @@ PROTOTYPES = {
     "mq_stack_tensors": (c_int, [_P, _L, _L, _I, _P, _P]),
     "mq_w4a16_grouped_gemm": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P]),
     "mq_w4a16_grouped_swiglu": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P]),
+    "mq_w4a16_stream_swiglu": (c_int, [_P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
+    "mq_w4a16_stream_gemm": (c_int, [_P, _P, _I, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P]),
     "mq_w4a16_tc_prep": (c_int, [_P, _P, _L, _L, _L, _I, _P, _P, _P]),
     "mq_w4a16_tc_gemm": (c_int, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P]),
     "mq_w4a16_tc_swiglu": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _P]),

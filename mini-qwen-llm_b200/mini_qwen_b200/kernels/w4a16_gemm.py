@@ -105,6 +105,57 @@ def w4a16_gemm(
                               qzeros.contiguous().unsqueeze(0), offsets, group_size, zero_init=False)
 
 
+# ---- prepared-activation forms of the stream kernel (the block's decode path) ------------------
+
+def w4a16_stream_supported(hidden: int, out_features: int, group_size: int, groups: int) -> bool:
+    """Shapes the TMA-staged stream kernel covers with prepared activations."""
+    return (group_size == 128 and hidden % 128 == 0 and hidden <= 4096 and out_features % 32 == 0
+            and groups <= 384)
+
+
+def w4a16_stream_swiglu(xp, xs, gate, up, expert_offsets, group_size: int = 128, x_shuffled: bool = True,
+                        shuffle_out: bool = True, status: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused gate/up + SwiGLU on prepared activations (``w4a16_tc_prep``): ``xp`` the expert-sorted rows in the
+    shuffled k order, ``xs`` their group sums (or None).  With ``shuffle_out`` the result's columns are in the
+    shuffled order, ready for :func:`w4a16_stream_gemm` with ``x_shuffled=True``."""
+    E = gate[0].shape[0]
+    K, N = _check_w4(xp, *gate, group_size, E)
+    _check_w4(xp, *up, group_size, E)
+    expert_offsets = _offsets32(expert_offsets)
+    groups = expert_offsets.numel() - 1
+    assert xp.is_contiguous() and (xs is None or (xs.is_contiguous() and xs.dtype == torch.float32))
+    S = xp.shape[0]
+    h = torch.empty(S, N, dtype=torch.bfloat16, device=xp.device)
+    rc = _cabi.load().mq_w4a16_stream_swiglu(
+        _cabi.ptr(xp), _cabi.ptr(xs), 1 if x_shuffled else 0, _cabi.ptr(gate[0]), _cabi.ptr(gate[1]), _cabi.ptr(gate[2]),
+        _cabi.ptr(up[0]), _cabi.ptr(up[1]), _cabi.ptr(up[2]), _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size,
+        1 if shuffle_out else 0, _cabi.ptr(h), _cabi.ptr(status), _cabi.stream_ptr(xp.device))
+    _cabi.check(rc, "mq_w4a16_stream_swiglu")
+    _cabi.count_launches(1 if S else 0)
+    return h
+
+
+def w4a16_stream_gemm(xp, xs, qweight, scales, qzeros, expert_offsets, group_size: int = 128, x_shuffled: bool = True,
+                      status: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One W4A16 projection per group on prepared activations; natural column order."""
+    E = qweight.shape[0]
+    K, N = _check_w4(xp, qweight, scales, qzeros, group_size, E)
+    expert_offsets = _offsets32(expert_offsets)
+    groups = expert_offsets.numel() - 1
+    assert xp.is_contiguous() and (xs is None or (xs.is_contiguous() and xs.dtype == torch.float32))
+    S = xp.shape[0]
+    if out is None:
+        out = torch.empty(S, N, dtype=torch.bfloat16, device=xp.device)
+    assert out.is_contiguous() and tuple(out.shape) == (S, N) and out.dtype == torch.bfloat16
+    rc = _cabi.load().mq_w4a16_stream_gemm(
+        _cabi.ptr(xp), _cabi.ptr(xs), 1 if x_shuffled else 0, _cabi.ptr(qweight), _cabi.ptr(scales), _cabi.ptr(qzeros),
+        _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size, _cabi.ptr(out), _cabi.ptr(status),
+        _cabi.stream_ptr(xp.device))
+    _cabi.check(rc, "mq_w4a16_stream_gemm")
+    _cabi.count_launches(1 if S else 0)
+    return out
+
+
 # ---- tcgen05 path for decode-size groups ------------------------------------------------------
 
 def w4a16_tc_supported(hidden: int, out_features: int, group_size: int) -> bool:

@@ -20,8 +20,9 @@ from ...kernels.moe_grouped_gemm import (gather_swiglu_supported, moe_grouped_ge
 from ...kernels.moe_permute import gather_rows, moe_permute_plan
 from ...kernels.moe_router import moe_router
 from ...kernels.moe_unpermute import unpermute_combine
-from ...kernels.w4a16_gemm import (w4a16_grouped_gemm, w4a16_grouped_swiglu, w4a16_tc_gemm, w4a16_tc_prep,
-                                     w4a16_tc_supported, w4a16_tc_swiglu)
+from ...kernels.w4a16_gemm import (w4a16_grouped_gemm, w4a16_grouped_swiglu, w4a16_stream_supported,
+                                     w4a16_stream_swiglu, w4a16_tc_gemm, w4a16_tc_prep, w4a16_tc_supported,
+                                     w4a16_tc_swiglu)
 from ... import parallel
 from .linear_w4a16 import LinearW4A16
 
@@ -76,9 +77,11 @@ class Qwen3MoEBlock(nn.Module):
         # "unique": a token row crosses NVLink once per destination rank and the owner's gate/up kernel
         # gathers through a slot table; "slots": one copy per slot (W4A16 experts, more than 8 ranks)
         self.ep_dispatch = "unique"
-        # W4A16 experts: "tc" = tcgen05 kernel with the weights dequantised into tensor memory (decode
-        # batches), "mma" = the mma.sync stream kernel, "auto" = by the number of slots per expert
-        self.w4_kernel = "mma"
+        # W4A16 experts: "stream" = activations prepared once (rows gathered in the k order the MMA wants, group
+        # sums), gate/up on the TMA-staged stream kernel, down on the cp.async kernel (the default);
+        # "mma" = both projections on the cp.async kernel from materialised rows; "tc" = the tcgen05 kernel
+        # with the weights dequantised into tensor memory; "auto" = "tc" by the number of slots per expert
+        self.w4_kernel = "stream"
         self._peer = None
         self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
         self.ep_rank = 0 if ep_group is None else torch.distributed.get_rank(ep_group)
@@ -197,6 +200,16 @@ class Qwen3MoEBlock(nn.Module):
             h = run("grouped_swiglu", moe_grouped_swiglu_gather, x2d, perm, K, st["w13"], off32, status=status)
             out_perm = run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False, status=status)
             return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K).reshape(shape)
+        if self.ep_size == 1 and st["w4"] and self._w4_stream(st):
+            # decode path: one preparation launch replaces the row gather, the gate/up kernel then needs no byte
+            # permutes and no extra MMAs for the group sums
+            status = self._status_word(x2d.device)
+            xp, xs = run("w4_prep", w4a16_tc_prep, x2d, perm, K)
+            h = run("grouped_swiglu", w4a16_stream_swiglu, xp, xs, st["gate_proj"], st["up_proj"], off32,
+                    st["group_size"], shuffle_out=False, status=status)
+            out_perm = run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off32, st["group_size"],
+                           zero_init=False)
+            return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K).reshape(shape)
         if self.ep_size == 1 and st["w4"] and self._w4_tc(st, T * K):
             # decode-size groups: weights dequantised into tensor memory, activations prepared once
             status = self._status_word(x2d.device)
@@ -230,9 +243,17 @@ class Qwen3MoEBlock(nn.Module):
         h = run("grouped_swiglu", moe_grouped_swiglu, rows, st["w13"], off32, zero_init=False, status=status)
         return run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False, out=out, status=status)
 
+    def _w4_stream(self, st) -> bool:
+        """Whether the prepared-activation path applies (``w4_kernel == "stream"`` and the shapes are covered)."""
+        if self.w4_kernel != "stream":
+            return False
+        H = st["gate_proj"][0].shape[1] * 8
+        I = st["gate_proj"][0].shape[2]
+        return w4a16_stream_supported(H, I, st["group_size"], self.num_local_experts)
+
     def _w4_tc(self, st, slots: int) -> bool:
         """Whether the W4A16 projections run on the tensor-memory kernel (``w4_kernel``: "auto", "tc", "mma")."""
-        if self.w4_kernel == "mma":
+        if self.w4_kernel in ("mma", "stream"):
             return False
         H = st["gate_proj"][0].shape[1] * 8
         I = st["gate_proj"][0].shape[2]

@@ -187,17 +187,20 @@ def dequantise(qweight, scales, qzeros, group_size: int = 128) -> torch.Tensor:
     return (q - z.repeat_interleave(group_size, 0)) * s.repeat_interleave(group_size, 0)
 
 
-def w4a16_linear(x, qweight, scales, qzeros, group_size: int = 128) -> torch.Tensor:
+def w4a16_linear(x, qweight, scales, qzeros, group_size: int = 128, accumulate=torch.float32) -> torch.Tensor:
     """x @ dequantised weight in fp32, result rounded to bf16
     (contract of mini_qwen/kernels/w4a16_gemm.py:8-15, checked the way
-    tests/test_w4a16_gemm.py:89-125 checks it)."""
-    return (x.float() @ dequantise(qweight, scales, qzeros, group_size)).to(torch.bfloat16)
+    tests/test_w4a16_gemm.py:89-125 checks it).  ``accumulate=torch.float64`` evaluates the same
+    product with exact sums (the dequantised weight is still the fp32 one): the yardstick for how far
+    the fp32 summation order alone moves the bf16 result."""
+    w = dequantise(qweight, scales, qzeros, group_size)
+    return (x.to(accumulate) @ w.to(accumulate)).to(torch.bfloat16)
 
 
-def w4a16_expert(x_e, gate, up, down, group_size: int = 128):
+def w4a16_expert(x_e, gate, up, down, group_size: int = 128, accumulate=torch.float32):
     """SwiGLU expert whose three projections are W4A16 linears; activations between them are
     bf16 as LinearW4A16.forward returns bf16 (linear_w4a16.py:31-36, moe.py:24-25).
     gate/up/down are (qweight, scales, qzeros) triples."""
-    g = w4a16_linear(x_e, *gate, group_size)
-    u = w4a16_linear(x_e, *up, group_size)
-    return w4a16_linear(F.silu(g) * u, *down, group_size)
+    g = w4a16_linear(x_e, *gate, group_size, accumulate)
+    u = w4a16_linear(x_e, *up, group_size, accumulate)
+    return w4a16_linear(F.silu(g) * u, *down, group_size, accumulate)

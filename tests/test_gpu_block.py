@@ -19,24 +19,6 @@ def cpu(t):
     return t.detach().cpu()
 
 
-def assert_block_close(out, ref):
-    """Output bar: |out - ref| <= atol + rtol * |ref| with rtol 2e-2, atol 2e-3.
-
-    The bar is met literally wherever outputs are O(1) (the bf16 configurations).  The W4A16
-    configuration produces outputs of magnitude 10-100 from bf16 intermediates, and elements that
-    nearly cancel then carry the bf16 rounding of terms 1000x larger: re-evaluating the reference
-    algorithm itself with exact (fp64) accumulation moves 0.2 % of its own outputs outside the
-    literal bar (max 0.125 at T=8).  For those the absolute term scales with the output
-    magnitude, and at least 99.5 % of all elements must meet the literal bar."""
-    out, ref = out.float(), ref.float()
-    err = (out - ref).abs()
-    literal = err <= ATOL + RTOL * ref.abs()
-    assert literal.float().mean().item() >= 0.995, f"only {literal.float().mean().item():.4f} within rtol/atol"
-    scaled = ATOL * max(1.0, ref.abs().max().item())
-    worst = (err - RTOL * ref.abs()).max().item()
-    assert worst <= scaled, f"error {worst} beyond {scaled} (atol scaled by the output magnitude)"
-
-
 def dense_block(lay, norm=True):
     E, I, H = lay.gate.shape
     cfg = Qwen3MoEConfig(hidden_size=H, intermediate_size=I, num_experts=E,
@@ -127,8 +109,16 @@ def test_block_config3_w4a16_decode(T):
     out = blk(x)
     assert out.dtype == torch.bfloat16 and out.shape == (T, 2048)
     ref = cases.from_bits(g[f"out_T{T}"], torch.bfloat16)
-    assert_block_close(cpu(out), ref)
-    assert torch.equal(blk(x), out)
+    ref64 = cases.w4_block_reference(lay, lay.x[:T], lay.router.to(torch.bfloat16), torch.float64)
+    for kernel in ("stream", "mma"):
+        blk.w4_kernel = kernel
+        got = blk(x)
+        shares = cases.w4_output_bar(cpu(got), ref, ref64)
+        print(f"\nC3 T={T} {kernel}: outside rtol/atol {shares[0]:.4%} (reference vs exact sums {shares[1]:.4%}); "
+              f"max distance from exact sums {shares[2]:.4g} (reference {shares[3]:.4g})")
+        assert torch.equal(blk(x), got)                     # deterministic across calls
+    blk.w4_kernel = "stream"
+    blk.check_status()
 
 
 def test_block_config4_skewed():
@@ -141,7 +131,13 @@ def test_block_config4_skewed():
     out = blk(x)
     ref_sample = cases.from_bits(g["out"], torch.bfloat16)
     torch.testing.assert_close(cpu(out[: cases.C4_SAMPLE_ROWS]).float(), ref_sample.float(), rtol=RTOL, atol=ATOL)
-    assert bool(torch.isfinite(out.float()).all())
+    # all 16384 rows against the oracle (groups of several thousand rows and empty groups are the point of
+    # this configuration)
+    ref, _, _, off = O.block_forward(lay.x, lay.router, lay.gate, lay.up, lay.down, lay.top_k, True, bias)
+    counts = off[1:] - off[:-1]
+    assert int((counts == 0).sum()) >= 1 and int(counts.max()) > 4096
+    torch.testing.assert_close(cpu(out).float(), ref.float(), rtol=RTOL, atol=ATOL)
+    blk.check_status()
 
 
 @pytest.mark.parametrize("i", range(len(cases.SCRIPT_CASES)))
@@ -176,12 +172,15 @@ def test_block_quantize_to_w4a16_on_device():
     bufs = {k: cpu(v) for k, v in blk.state_dict().items()}
     assert set(k.rsplit(".", 1)[1] for k in bufs if "experts" in k) == {"qweight", "scales", "qzeros"}
 
-    def fn(e, x_e):
-        trios = [tuple(bufs[f"experts.{e}.{p}.{b}"] for b in ("qweight", "scales", "qzeros"))
-                 for p in ("gate_proj", "up_proj", "down_proj")]
-        return O.w4a16_expert(x_e, *trios, 32)
-    ref, *_ = O.block_forward(x, dense_sd["gate.weight"], None, None, None, 4, True, expert_fn=fn)
-    assert_block_close(cpu(out), ref)
+    def expert(accumulate):
+        def fn(e, x_e):
+            trios = [tuple(bufs[f"experts.{e}.{p}.{b}"] for b in ("qweight", "scales", "qzeros"))
+                     for p in ("gate_proj", "up_proj", "down_proj")]
+            return O.w4a16_expert(x_e, *trios, 32, accumulate)
+        return fn
+    ref, *_ = O.block_forward(x, dense_sd["gate.weight"], None, None, None, 4, True, expert_fn=expert(torch.float32))
+    ref64, *_ = O.block_forward(x, dense_sd["gate.weight"], None, None, None, 4, True, expert_fn=expert(torch.float64))
+    cases.w4_output_bar(cpu(out), ref, ref64)
     qw_cpu, _, _ = O.minmax_quantize(dense_sd["experts.3.up_proj.weight"].float().T.contiguous(), 32)
     assert (O.unpack_int4(qw_cpu) != O.unpack_int4(bufs["experts.3.up_proj.qweight"])).float().mean() < 0.05
 
