@@ -92,6 +92,29 @@ int mq_router_topk_static(const void* x, int x_dtype, const void* w, int w_dtype
                           int64_t* ids64, int32_t* ids32, float* weights, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Router + permute plan (+ activation preparation) for small batches, in one launch.  Replaces, for decode
+ * batches, the chain moe_router -> renormalise -> index work of moe_permute (mini_qwen/model/layers/moe.py:
+ * 54-57) that the calls above and below make in three launches (plus mq_w4a16_tc_prep): at these sizes the
+ * layer call is bound by its chain of launches.  Same ids, weights, perm, inv and offsets as mq_router_topk
+ * followed by mq_permute_plan (the logits are summed in the order of the few-token logits kernel).
+ *   workspace: mq_route_small_workspace_bytes(T, E) bytes, 16-byte aligned, ZERO-FILLED ONCE by the caller
+ *     after allocating it (it holds the logits and a counter the kernel leaves at zero again); calls that share
+ *     a workspace must not overlap on the GPU;
+ *   ids32 int32 [T,K] (required), ids64 int64 [T,K] (optional), weights fp32 [T,K], perm/inv int32 [T*K],
+ *     offsets64 / offsets32 [E+1] (one may be NULL);
+ *   xp bf16 [T,H] and xs fp32 [T,32], both or neither: every token row in the k order 0,4,1,5,2,6,3,7 inside
+ *     every 8 and its sums over every 128 k, the per-token form of what mq_w4a16_tc_prep writes (bf16 x only,
+ *     H % 128 == 0, H <= 4096).
+ * Limits: T <= 64, E <= 256, K <= 32, T*K <= 2048 (MQ_ERR_UNSUPPORTED_SHAPE otherwise).
+ */
+size_t mq_route_small_workspace_bytes(int64_t T, int64_t E);
+int mq_route_small(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
+                   int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
+                   void* workspace, size_t workspace_bytes, int64_t* ids64, int32_t* ids32,
+                   float* weights, int32_t* perm, int32_t* inv, int64_t* offsets64, int32_t* offsets32,
+                   void* xp, float* xs, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Permute plan.  Replaces the index work of moe_permute / moe_unpermute
  * (mini_qwen/kernels/moe_permute.py:22-27, moe_unpermute.py:23-25): a stable counting sort of
  * the S = T*K flat slots by expert id.
@@ -221,10 +244,12 @@ int mq_w4a16_grouped_swiglu(const void* x,
  *   xs fp32 [S,32] or NULL: the rows' sums over every quantisation group (mq_w4a16_tc_prep); given, the
  *     kernel skips the extra MMA pair per 32 k that otherwise forms them; requires x_shuffled;
  *   shuffle_out != 0: h is written with its columns in the shuffled order, ready to be the xp of the down
- *     projection (pass x_shuffled = 1 there).
+ *     projection (pass x_shuffled = 1 there);
+ *   perm (mq_w4a16_stream_swiglu, optional): xp and xs then hold one row per TOKEN and row p of the expert-sorted
+ *     order is row perm[p] / top_k of them, gathered inside the kernel (what mq_route_small prepares).
  * group_size == 128, N % 32 == 0, at most 384 row groups (MQ_ERR_UNSUPPORTED_SHAPE otherwise).  d_status
  * (optional) receives MQ_DEV_WAIT_EXPIRED if a bounded wait on a bulk copy ran out. */
-int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shuffled,
+int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shuffled, const int32_t* perm, int64_t top_k,
                            const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
                            const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
                            const int32_t* offsets, int64_t S, int64_t E, int64_t weight_period, int64_t I,

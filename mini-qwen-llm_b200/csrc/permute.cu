@@ -6,6 +6,7 @@
 // here the keys have at most 1024 distinct values, so a histogram + prefix scan + ranked placement
 // gives the same permutation: within an expert, slots keep ascending flat index t*K+k.
 #include "common.cuh"
+#include "route_helpers.cuh"
 
 namespace mq {
 namespace {
@@ -16,77 +17,6 @@ constexpr int P_SEG = P_CHUNK;            // slots per CTA in the multi-CTA plan
 constexpr int P_SMALL = 8 * P_CHUNK;      // up to this many slots the whole plan runs in one CTA
 constexpr int P_MAX_E = 1024;
 
-template <bool IDS64>
-__device__ __forceinline__ int load_id(const void* ids, int64_t i) {
-  if (IDS64) return (int)reinterpret_cast<const int64_t*>(ids)[i];
-  return reinterpret_cast<const int32_t*>(ids)[i];
-}
-
-// Exclusive scan over v[0..E) in shared memory (E <= 1024), 256 threads; returns the total.
-__device__ int block_exclusive_scan(int* v, int E, int* warp_tot /* shared [8] */) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  int local[4];
-  int sum = 0;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    int e = tid * 4 + j;
-    local[j] = (e < E) ? v[e] : 0;
-    sum += local[j];
-  }
-  int incl = sum;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    int n = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += n;
-  }
-  if (lane == 31) warp_tot[warp] = incl;
-  __syncthreads();
-  int base = 0, total = 0;
-#pragma unroll
-  for (int wi = 0; wi < P_THREADS / 32; ++wi) {
-    int wt = warp_tot[wi];
-    if (wi < warp) base += wt;
-    total += wt;
-  }
-  int run = base + incl - sum;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    int e = tid * 4 + j;
-    if (e < E) v[e] = run;
-    run += local[j];
-  }
-  __syncthreads();
-  return total;
-}
-
-// Ranks the slots [seg_lo, seg_hi) in ascending order; run[e] holds the next free sorted
-// position of expert e on entry and is advanced.  One warp at a time touches run[], which keeps
-// the placement stable without atomics.
-template <bool IDS64>
-__device__ void place_segment(const void* ids, int64_t seg_lo, int64_t seg_hi, int E, int* run,
-                              int32_t* perm, int32_t* inv) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int64_t c0 = seg_lo; c0 < seg_hi; c0 += P_CHUNK) {
-    const int64_t i = c0 + tid;
-    int e = -1;
-    if (i < seg_hi) {
-      e = load_id<IDS64>(ids, i);
-      if ((unsigned)e >= (unsigned)E) e = -1;   // an id outside [0,E) is left unplaced
-    }
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
-    const int rank = __popc(peers & ((1u << lane) - 1u));
-    for (int wi = 0; wi < P_THREADS / 32; ++wi) {
-      if (warp == wi && e >= 0) {
-        const int pos = run[e] + rank;
-        __syncwarp(peers);
-        if (rank == 0) run[e] += __popc(peers);
-        perm[pos] = (int32_t)i;
-        inv[i] = pos;
-      }
-      __syncthreads();
-    }
-  }
-}
 
 template <bool IDS64>
 __global__ void __launch_bounds__(P_THREADS)
@@ -140,7 +70,7 @@ permute_place(const void* __restrict__ ids, int64_t S, int E, int nseg, const in
   __shared__ int warp_tot[P_THREADS / 32];
   for (int e = threadIdx.x; e < E; e += P_THREADS) run[e] = totals[e];
   __syncthreads();
-  const int total = block_exclusive_scan(run, E, warp_tot);
+  const int total = block_exclusive_scan<P_THREADS>(run, E, warp_tot);
   if (blockIdx.x == 0) {
     for (int e = threadIdx.x; e < E; e += P_THREADS) {
       if (off64) off64[e] = run[e];
@@ -154,7 +84,7 @@ permute_place(const void* __restrict__ ids, int64_t S, int E, int nseg, const in
   for (int e = threadIdx.x; e < E; e += P_THREADS) run[e] += seg_base[(size_t)e * nseg + blockIdx.x];
   __syncthreads();
   const int64_t lo = (int64_t)blockIdx.x * P_SEG;
-  place_segment<IDS64>(ids, lo, min(lo + (int64_t)P_SEG, S), E, run, perm, inv);
+  place_segment<IDS64, P_THREADS>(ids, lo, min(lo + (int64_t)P_SEG, S), E, run, perm, inv);
 }
 
 // Whole plan in one CTA when all slots fit one segment (decode batches).
@@ -171,7 +101,7 @@ permute_plan_small(const void* __restrict__ ids, int64_t S, int E, int32_t* __re
     if ((unsigned)e < (unsigned)E) atomicAdd(&run[e], 1);
   }
   __syncthreads();
-  int total = block_exclusive_scan(run, E, warp_tot);
+  int total = block_exclusive_scan<P_THREADS>(run, E, warp_tot);
   for (int e = threadIdx.x; e < E; e += P_THREADS) {
     if (off64) off64[e] = run[e];
     if (off32) off32[e] = run[e];
@@ -181,7 +111,7 @@ permute_plan_small(const void* __restrict__ ids, int64_t S, int E, int32_t* __re
     if (off32) off32[E] = total;
   }
   __syncthreads();
-  place_segment<IDS64>(ids, 0, S, E, run, perm, inv);
+  place_segment<IDS64, P_THREADS>(ids, 0, S, E, run, perm, inv);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "route_helpers.cuh"
 
 namespace mq {
 namespace {
@@ -340,17 +341,6 @@ router_logits_skinny(const void* __restrict__ x, int xdt, const void* __restrict
 }
 
 // ---------------------------------------------------------------------------------------------
-template <int NS>
-__device__ __forceinline__ float sum_slices(const float* p, size_t stride) {
-  float part[NS];
-#pragma unroll
-  for (int sl = 0; sl < NS; ++sl) part[sl] = p[sl * stride];
-  float v = part[0];
-#pragma unroll
-  for (int sl = 1; sl < NS; ++sl) v += part[sl];
-  return v;
-}
-
 // One warp per token: softmax over E logits, then K rounds of warp arg-max on (score, -id).
 template <int EPL>
 __global__ void __launch_bounds__(128)
@@ -360,73 +350,155 @@ router_softmax_topk(const float* __restrict__ logits, int slices, const float* _
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (t >= T) return;
+  softmax_topk_row<EPL>(logits + (size_t)t * E, slices, (size_t)T * E, bias, E, K, renorm, lane,
+                        ids64 ? ids64 + t * K : nullptr, ids32 ? ids32 + t * K : nullptr, weights + t * K);
+}
 
-  float s[EPL];
-  float m = -INFINITY;
+// ---------------------------------------------------------------------------------------------
+// Small batches (decode): logits, softmax + top-k, the permute plan and the preparation of the activations
+// for the W4A16 kernels in ONE launch.  At these sizes each of the four kernels runs for a few microseconds
+// and the layer call is bound by the chain of launches, not by any of them.
+//   phase A, every CTA: CTA e forms the logits of expert e for all tokens with the arithmetic of
+//     router_logits_skinny (fp32 FMA chains over lanes' 8-element pieces, shuffle tree), and CTA t < T
+//     also writes token t's row in the k order the W4A16 kernels want, with its group sums;
+//   phase B, the CTA that finishes last (a counter in the workspace tells it; nobody waits): softmax and
+//     top-k of every token (one warp per token, softmax_topk_row), then the stable counting sort of the
+//     T*K slots (the code of permute_plan_small).  It leaves the counter at zero for the next call.
+constexpr int RSM_THREADS = 512;
+constexpr int RSM_MAX_T = 64, RSM_MAX_E = 256, RSM_MAX_S = 2048;
+
+template <int EPL>
+__global__ void __launch_bounds__(RSM_THREADS)
+route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__ w, int wdt,
+                   const float* __restrict__ bias, int T, int H, int E, int K, int renorm, int vec_ok,
+                   float* __restrict__ logits, int* __restrict__ counter,
+                   int32_t* __restrict__ ids32, int64_t* __restrict__ ids64, float* __restrict__ weights,
+                   int32_t* __restrict__ perm, int32_t* __restrict__ inv, int32_t* __restrict__ off32,
+                   int64_t* __restrict__ off64, __nv_bfloat16* __restrict__ xp, float* __restrict__ xs) {
+  extern __shared__ __align__(16) uint8_t rsm_smem[];
+  __shared__ int s_last;
+  __shared__ int s_warp_tot[RSM_THREADS / 32];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int e = blockIdx.x;
+
+  // ---- phase A: logits of expert e
+  {
+    const size_t w_row = (size_t)e * H;
+    const bool fast = vec_ok && xdt != MQ_F32 && wdt != MQ_F32;     // 16-bit operands, 16-byte pieces
+    for (int tb = warp * 8; tb < T; tb += (RSM_THREADS / 32) * 8) {
+      float acc[8];
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    int e = lane + 32 * j;
-    float v = -INFINITY;
-    if (e < E) {
-      // the K slices are summed in ascending order; the usual counts are unrolled (loads first, then adds)
-      const float* p = logits + (size_t)t * E + e;
-      const size_t stride = (size_t)T * E;
-      if (slices == 1) v = sum_slices<1>(p, stride);
-      else if (slices == 2) v = sum_slices<2>(p, stride);
-      else if (slices == 3) v = sum_slices<3>(p, stride);
-      else if (slices == 4) v = sum_slices<4>(p, stride);
-      else {
-        v = p[0];
-        for (int sl = 1; sl < slices; ++sl) v += p[sl * stride];
+      for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+      if (fast) {
+        const uint16_t* wp = reinterpret_cast<const uint16_t*>(w) + w_row;
+        const uint16_t* xq = reinterpret_cast<const uint16_t*>(x);
+        for (int k = lane * 8; k < H; k += 32 * 8) {
+          const uint4 wr = __ldg(reinterpret_cast<const uint4*>(wp + k));
+          uint4 xr[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            xr[i] = tb + i < T ? __ldg(reinterpret_cast<const uint4*>(xq + (size_t)(tb + i) * H + k)) : make_uint4(0, 0, 0, 0);
+          float wv[8];
+          unpack8_16bit(wr, wdt == MQ_BF16, wv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float xv[8];
+            unpack8_16bit(xr[i], xdt == MQ_BF16, xv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[i] = fmaf(xv[j], wv[j], acc[i]);
+          }
+        }
+      } else {
+        for (int64_t k = (int64_t)lane * 8; k < H; k += 32 * 8) {
+          float wv[8];
+          load8_safe(w, wdt, w_row, k, H, vec_ok, wv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (tb + i < T) {
+              float xv[8];
+              load8_safe(x, xdt, (size_t)(tb + i) * H, k, H, vec_ok, xv);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[i] = fmaf(xv[j], wv[j], acc[i]);
+            }
+          }
+        }
       }
-      if (bias != nullptr) v += bias[e];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float v = acc[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && tb + i < T) logits[(size_t)(tb + i) * E + e] = v;
+      }
     }
-    s[j] = v;
-    m = fmaxf(m, v);
   }
+  // ---- phase A: token row e in the k order 0,4,1,5,2,6,3,7 inside every 8, and its sums over every 128 k
+  // (the arithmetic of the stand-alone preparation kernel: eight adds per 16-byte piece, then a shuffle
+  // tree over the 16 lanes of a group)
+  if (xp != nullptr && e < T) {
+    const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)e * H);
+    uint4* o = reinterpret_cast<uint4*>(xp + (size_t)e * H);
+    for (int c0 = warp * 32; c0 < H / 8; c0 += RSM_THREADS) {
+      const int c = c0 + lane;
+      float sum = 0.0f;
+      if (c < H / 8) {
+        const uint4 v = in[c];
+        const uint16_t* hh = reinterpret_cast<const uint16_t*>(&v);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  float sum = 0.0f;
+        for (int j = 0; j < 8; ++j) sum += __bfloat162float(__ushort_as_bfloat16(hh[j]));
+        uint4 sh;
+        sh.x = (uint32_t)hh[0] | ((uint32_t)hh[4] << 16);
+        sh.y = (uint32_t)hh[1] | ((uint32_t)hh[5] << 16);
+        sh.z = (uint32_t)hh[2] | ((uint32_t)hh[6] << 16);
+        sh.w = (uint32_t)hh[3] | ((uint32_t)hh[7] << 16);
+        o[c] = sh;
+      }
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) {
-    int e = lane + 32 * j;
-    float p = (e < E) ? expf(s[j] - m) : 0.0f;
-    s[j] = p;
-    sum += p;
+      for (int d = 8; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+      if ((lane & 15) == 0 && c < H / 8) xs[(size_t)e * 32 + (c >> 4)] = sum;
+    }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) s[j] = (lane + 32 * j < E) ? s[j] / sum : -1.0f;  // scores >= 0; -1 = absent
 
-  uint32_t taken = 0;
-  float my_w = 0.0f;
-  int my_id = 0;
-  float wsum = 0.0f;
-  for (int k = 0; k < K; ++k) {
-    float best = -2.0f;
-    int best_e = 0x7fffffff;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      // ascending j = ascending id within the lane, strict > keeps the lower id on ties
-      if (!((taken >> j) & 1u) && s[j] > best) { best = s[j]; best_e = lane + 32 * j; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-    }
-    if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
-    if (lane == k) { my_w = best; my_id = best_e; }
-    wsum += best;
+  // ---- who is last?
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(counter, 1) == (int)gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+
+  // ---- phase B: the logits of all experts come from L2 into shared memory, then one warp per token
+  float* s_logits = reinterpret_cast<float*>(rsm_smem);                 // [T, E]
+  int* s_ids = reinterpret_cast<int*>(rsm_smem + (size_t)T * E * 4);     // [T * K]
+  int* s_run = s_ids + T * K;                                           // [E]
+  for (int i = tid; i < T * E; i += RSM_THREADS) s_logits[i] = __ldcg(logits + i);
+  __syncthreads();
+  for (int t = warp; t < T; t += RSM_THREADS / 32)
+    softmax_topk_row<EPL>(s_logits + (size_t)t * E, 1, 0, bias, E, K, renorm, lane,
+                          ids64 ? ids64 + (size_t)t * K : nullptr, s_ids + t * K, weights + (size_t)t * K);
+  __syncthreads();
+  const int S = T * K;
+  for (int i = tid; i < S; i += RSM_THREADS) ids32[i] = s_ids[i];
+  // the plan: histogram, exclusive scan, stable placement
+  for (int ee = tid; ee < E; ee += RSM_THREADS) s_run[ee] = 0;
+  __syncthreads();
+  for (int i = tid; i < S; i += RSM_THREADS) {
+    const int ee = s_ids[i];
+    if ((unsigned)ee < (unsigned)E) atomicAdd(&s_run[ee], 1);
   }
-  if (lane < K) {
-    float wv = renorm ? my_w / wsum : my_w;
-    weights[t * K + lane] = wv;
-    if (ids64 != nullptr) ids64[t * K + lane] = my_id;
-    if (ids32 != nullptr) ids32[t * K + lane] = my_id;
+  __syncthreads();
+  const int total = block_exclusive_scan<RSM_THREADS>(s_run, E, s_warp_tot);
+  for (int ee = tid; ee < E; ee += RSM_THREADS) {
+    if (off64) off64[ee] = s_run[ee];
+    if (off32) off32[ee] = s_run[ee];
   }
+  if (tid == 0) {
+    if (off64) off64[E] = total;
+    if (off32) off32[E] = total;
+    *counter = 0;                                   // ready for the next call
+  }
+  __syncthreads();
+  place_segment<false, RSM_THREADS>(s_ids, 0, S, E, s_run, perm, inv);
 }
 
 template <int EPL>
@@ -587,4 +659,47 @@ extern "C" int mq_router_topk_static(const void* x, int x_dtype, const void* w, 
   // them, so nothing in the array has to start at zero and the previous call's contents are harmless.
   return mq_router_topk(x, x_dtype, w, w_dtype, bias, T, H, E, K, renormalize, scratch, R_STATIC_SCRATCH_BYTES,
                         ids64, ids32, weights, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+extern "C" size_t mq_route_small_workspace_bytes(int64_t T, int64_t E) {
+  if (T <= 0 || E <= 0) return 16;
+  return (size_t)T * (size_t)E * sizeof(float) + 16;
+}
+
+extern "C" int mq_route_small(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
+                              int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
+                              void* workspace, size_t workspace_bytes, int64_t* ids64, int32_t* ids32,
+                              float* weights, int32_t* perm, int32_t* inv, int64_t* offsets64, int32_t* offsets32,
+                              void* xp, float* xs, void* stream) {
+  using namespace mq;
+  if (T < 0 || H <= 0 || E <= 0 || K <= 0) return MQ_ERR_INVALID_ARGUMENT;
+  if (!valid_dtype(x_dtype) || !valid_dtype(w_dtype)) return MQ_ERR_INVALID_ARGUMENT;
+  if (K > E || K > 32 || T > RSM_MAX_T || E > RSM_MAX_E || T * K > RSM_MAX_S) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if ((xp != nullptr) != (xs != nullptr)) return MQ_ERR_INVALID_ARGUMENT;
+  // the prepared rows are a bf16 format with 128-k groups, 32 of them at most
+  if (xp != nullptr && (x_dtype != MQ_BF16 || H % 128 != 0 || H / 128 > 32)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (T == 0) return MQ_OK;
+  if (!x || !w || !workspace || !weights || !ids32 || !perm || !inv || (!offsets64 && !offsets32))
+    return MQ_ERR_INVALID_ARGUMENT;
+  if (workspace_bytes < mq_route_small_workspace_bytes(T, E) || !aligned16(workspace)) return MQ_ERR_WORKSPACE_TOO_SMALL;
+  if (xp != nullptr && (!aligned16(x) || !aligned16(xp))) return MQ_ERR_INVALID_ARGUMENT;
+  const int vec_ok = (H % 8 == 0) && aligned16(x) && aligned16(w);
+  float* logits = reinterpret_cast<float*>(workspace);
+  int* counter = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + (size_t)T * E * sizeof(float));
+  const size_t smem = (size_t)T * E * 4 + (size_t)T * K * 4 + (size_t)E * 4;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define MQ_RSM_LAUNCH(EPL)                                                                                       \
+  do {                                                                                                           \
+    cudaFuncSetAttribute(route_small_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+    route_small_kernel<EPL><<<(unsigned)E, RSM_THREADS, smem, st>>>(                                              \
+        x, x_dtype, w, w_dtype, bias, (int)T, (int)H, (int)E, (int)K, renormalize, vec_ok, logits, counter, ids32, \
+        ids64, weights, perm, inv, offsets32, offsets64, reinterpret_cast<__nv_bfloat16*>(xp), xs);               \
+  } while (0)
+  if (E <= 32) MQ_RSM_LAUNCH(1);
+  else if (E <= 64) MQ_RSM_LAUNCH(2);
+  else if (E <= 128) MQ_RSM_LAUNCH(4);
+  else MQ_RSM_LAUNCH(8);
+#undef MQ_RSM_LAUNCH
+  return check_launch();
 }

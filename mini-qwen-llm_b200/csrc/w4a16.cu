@@ -441,8 +441,8 @@ extern "C" int mq_w4a16_grouped_swiglu(const void* x,
 }
 
 /* Prepared-activation forms: see include/mqmoe.h. */
-extern "C" int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shuffled,
-                                      const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
+extern "C" int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shuffled, const int32_t* perm,
+                                      int64_t top_k, const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
                                       const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
                                       const int32_t* offsets, int64_t S, int64_t E, int64_t weight_period, int64_t I,
                                       int64_t H, int64_t group_size, int shuffle_out, void* h, int32_t* d_status,
@@ -450,9 +450,10 @@ extern "C" int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shu
   mq::W4Proj pg{qweight_gate, reinterpret_cast<const __nv_bfloat16*>(scales_gate), qzeros_gate};
   mq::W4Proj pu{qweight_up, reinterpret_cast<const __nv_bfloat16*>(scales_up), qzeros_up};
   if (!mq::w4a16_stream_covers(S, E, weight_period, I, H, group_size)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (perm != nullptr && top_k <= 0) return MQ_ERR_INVALID_ARGUMENT;
   return mq::launch_w4(xp, pg, pu, true, offsets, S, E, weight_period, I, H, group_size, h,
-                       reinterpret_cast<cudaStream_t>(stream), nullptr, 1, d_status, xs, x_shuffled != 0,
-                       shuffle_out != 0, true);
+                       reinterpret_cast<cudaStream_t>(stream), perm, perm != nullptr ? top_k : 1, d_status, xs,
+                       x_shuffled != 0, shuffle_out != 0, true);
 }
 
 extern "C" int mq_w4a16_stream_gemm(const void* xp, const float* xs, int x_shuffled, const int32_t* qweight,

@@ -114,20 +114,25 @@ def w4a16_stream_supported(hidden: int, out_features: int, group_size: int, grou
 
 
 def w4a16_stream_swiglu(xp, xs, gate, up, expert_offsets, group_size: int = 128, x_shuffled: bool = True,
-                        shuffle_out: bool = True, status: torch.Tensor | None = None) -> torch.Tensor:
+                        shuffle_out: bool = True, status: torch.Tensor | None = None,
+                        perm: torch.Tensor | None = None, top_k: int = 1) -> torch.Tensor:
     """Fused gate/up + SwiGLU on prepared activations (``w4a16_tc_prep``): ``xp`` the expert-sorted rows in the
     shuffled k order, ``xs`` their group sums (or None).  With ``shuffle_out`` the result's columns are in the
-    shuffled order, ready for :func:`w4a16_stream_gemm` with ``x_shuffled=True``."""
+    shuffled order, ready for :func:`w4a16_stream_gemm` with ``x_shuffled=True``.  With ``perm`` (int32 [S]),
+    ``xp``/``xs`` hold one row per token and sorted row p is row ``perm[p] // top_k`` (``moe_route_small``)."""
     E = gate[0].shape[0]
     K, N = _check_w4(xp, *gate, group_size, E)
     _check_w4(xp, *up, group_size, E)
     expert_offsets = _offsets32(expert_offsets)
     groups = expert_offsets.numel() - 1
     assert xp.is_contiguous() and (xs is None or (xs.is_contiguous() and xs.dtype == torch.float32))
-    S = xp.shape[0]
+    S = xp.shape[0] if perm is None else perm.numel()
+    if perm is not None:
+        assert perm.dtype == torch.int32 and perm.is_contiguous() and top_k >= 1
     h = torch.empty(S, N, dtype=torch.bfloat16, device=xp.device)
     rc = _cabi.load().mq_w4a16_stream_swiglu(
-        _cabi.ptr(xp), _cabi.ptr(xs), 1 if x_shuffled else 0, _cabi.ptr(gate[0]), _cabi.ptr(gate[1]), _cabi.ptr(gate[2]),
+        _cabi.ptr(xp), _cabi.ptr(xs), 1 if x_shuffled else 0, _cabi.ptr(perm), top_k,
+        _cabi.ptr(gate[0]), _cabi.ptr(gate[1]), _cabi.ptr(gate[2]),
         _cabi.ptr(up[0]), _cabi.ptr(up[1]), _cabi.ptr(up[2]), _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size,
         1 if shuffle_out else 0, _cabi.ptr(h), _cabi.ptr(status), _cabi.stream_ptr(xp.device))
     _cabi.check(rc, "mq_w4a16_stream_swiglu")

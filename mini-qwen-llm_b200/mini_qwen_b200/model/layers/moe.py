@@ -18,7 +18,7 @@ import torch.nn as nn
 from ...kernels.moe_grouped_gemm import (gather_swiglu_supported, moe_grouped_gemm, moe_grouped_gemm_scatter,
                                           moe_grouped_swiglu, moe_grouped_swiglu_gather, scatter_gemm_supported)
 from ...kernels.moe_permute import gather_rows, moe_permute_plan
-from ...kernels.moe_router import moe_router
+from ...kernels.moe_router import moe_route_small, moe_router, route_small_supported, route_small_workspace
 from ...kernels.moe_unpermute import unpermute_combine
 from ...kernels.w4a16_gemm import (w4a16_grouped_gemm, w4a16_grouped_swiglu, w4a16_stream_supported,
                                      w4a16_stream_swiglu, w4a16_tc_gemm, w4a16_tc_prep, w4a16_tc_supported,
@@ -82,6 +82,13 @@ class Qwen3MoEBlock(nn.Module):
         # "mma" = both projections on the cp.async kernel from materialised rows; "tc" = the tcgen05 kernel
         # with the weights dequantised into tensor memory; "auto" = "tc" by the number of slots per expert
         self.w4_kernel = "stream"
+        # small batches: router, top-k, permute plan (and the W4A16 activation preparation) as ONE launch
+        # instead of three or four (single GPU; same ids and plan, weights equal up to the order of the fp32 logit sums).  The last CTA to finish does the
+        # top-k and the plan on its own, which pays up to 16 tokens (batch 1: 42.7 against 45.5 us per layer
+        # call) and costs from there on (batch 64: 152.7 against 146.8 us)
+        self.fuse_small_batches = True
+        self.fuse_max_tokens = 16
+        self._route_ws = None
         self._peer = None
         self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
         self.ep_rank = 0 if ep_group is None else torch.distributed.get_rank(ep_group)
@@ -172,6 +179,41 @@ class Qwen3MoEBlock(nn.Module):
         blk._stacked_sentinel = blk._sentinel()
         return blk
 
+    @classmethod
+    def from_stacked_w4(cls, config, router_weight: torch.Tensor, gate, up, down, group_size: int = 128,
+                        ep_group=None, ep_mode: str = "p2p", ep_max_tokens: int | None = None) -> "Qwen3MoEBlock":
+        """Builds a W4A16 block from expert-major stacks without copying them.  ``gate``, ``up`` and ``down``
+        are ``(qweight [E, K/8, N] int32, scales [E, K/g, N] bf16, qzeros [E, K/g, N/8] int32)`` in the
+        convention of the module buffers, i.e. what ``LinearW4A16.from_gptq`` stores (bf16 scales, zero
+        points already incremented and clamped).  The per-expert ``LinearW4A16`` modules become views of the
+        stacks.  With ``ep_group`` the stacks hold this rank's experts only; the router weight covers all."""
+        with torch.device("meta"):
+            blk = cls(config, ep_group=ep_group, ep_mode=ep_mode, ep_max_tokens=ep_max_tokens)
+        E = blk.num_local_experts
+        H, I = config.hidden_size, config.intermediate_size
+        shapes = {"gate_proj": (H, I), "up_proj": (H, I), "down_proj": (I, H)}
+        stacks = {"w4": True, "group_size": group_size}
+        for name, trio in (("gate_proj", gate), ("up_proj", up), ("down_proj", down)):
+            kd, n = shapes[name]
+            qw, sc, qz = (t.contiguous() for t in trio)
+            assert tuple(qw.shape) == (E, kd // 8, n) and qw.dtype == torch.int32, f"{name}: qweight {tuple(qw.shape)}"
+            assert tuple(sc.shape) == (E, kd // group_size, n) and sc.dtype == torch.bfloat16, f"{name}: scales"
+            assert tuple(qz.shape) == (E, kd // group_size, n // 8) and qz.dtype == torch.int32, f"{name}: qzeros"
+            stacks[name] = (qw, sc, qz)
+        assert tuple(router_weight.shape) == (config.num_experts, H)
+        blk.gate.weight = nn.Parameter(router_weight, requires_grad=False)
+        for e, ex in enumerate(blk.experts):
+            for name, (kd, n) in shapes.items():
+                with torch.device("meta"):
+                    lin = LinearW4A16(kd, n, group_size)
+                for buf, st in zip(("qweight", "scales", "qzeros"), stacks[name]):
+                    lin._buffers[buf] = st[e]
+                setattr(ex, name, lin)
+        blk._stacks = stacks
+        blk._stacked_epoch = blk._epoch[0]
+        blk._stacked_sentinel = blk._sentinel()
+        return blk
+
     def _ready(self):
         if (self._stacks is None or self._stacked_epoch != self._epoch[0]
                 or self._stacked_sentinel != self._sentinel()):
@@ -189,9 +231,20 @@ class Qwen3MoEBlock(nn.Module):
         st = self._ready()
 
         run = self._stage
-        _, weights, ids32 = run("router", moe_router, x2d, self.gate.weight, K, bias=self.router_bias,
-                                renormalize=self.norm_topk_prob, return_int32_ids=True)
-        perm, inv, off32, _ = run("permute_plan", moe_permute_plan, ids32, E, want_int64_offsets=False)
+        xp_tok = xs_tok = None
+        if (self.fuse_small_batches and self.ep_size == 1 and T <= self.fuse_max_tokens
+                and route_small_supported(T, E, K)):
+            # decode batches: logits, top-k, plan and the W4A16 activation preparation in one launch
+            prepare = st["w4"] and x2d.dtype == torch.bfloat16 and self._w4_stream(st)
+            if self._route_ws is None or self._route_ws.device != x2d.device:
+                self._route_ws = route_small_workspace(E, x2d.device)     # zero-filled once, reused by every call
+            ids32, weights, perm, inv, off32, xp_tok, xs_tok = run(
+                "route_small", moe_route_small, x2d, self.gate.weight, K, bias=self.router_bias,
+                renormalize=self.norm_topk_prob, prepare=prepare, workspace=self._route_ws)
+        else:
+            _, weights, ids32 = run("router", moe_router, x2d, self.gate.weight, K, bias=self.router_bias,
+                                    renormalize=self.norm_topk_prob, return_int32_ids=True)
+            perm, inv, off32, _ = run("permute_plan", moe_permute_plan, ids32, E, want_int64_offsets=False)
         if self.ep_size > 1 and self.ep_mode == "p2p":
             return self._forward_peer(x2d, st, weights, ids32, perm, inv, off32, T, K, E).reshape(shape)
         if self.ep_size == 1 and not st["w4"] and gather_swiglu_supported(x2d, st["w13"]):
@@ -204,9 +257,14 @@ class Qwen3MoEBlock(nn.Module):
             # decode path: one preparation launch replaces the row gather, the gate/up kernel then needs no byte
             # permutes and no extra MMAs for the group sums
             status = self._status_word(x2d.device)
-            xp, xs = run("w4_prep", w4a16_tc_prep, x2d, perm, K)
-            h = run("grouped_swiglu", w4a16_stream_swiglu, xp, xs, st["gate_proj"], st["up_proj"], off32,
-                    st["group_size"], shuffle_out=False, status=status)
+            if xp_tok is not None:
+                # prepared per token by the routing launch: the gate/up kernel gathers through the permutation
+                h = run("grouped_swiglu", w4a16_stream_swiglu, xp_tok, xs_tok, st["gate_proj"], st["up_proj"], off32,
+                        st["group_size"], shuffle_out=False, status=status, perm=perm, top_k=K)
+            else:
+                xp, xs = run("w4_prep", w4a16_tc_prep, x2d, perm, K)
+                h = run("grouped_swiglu", w4a16_stream_swiglu, xp, xs, st["gate_proj"], st["up_proj"], off32,
+                        st["group_size"], shuffle_out=False, status=status)
             out_perm = run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off32, st["group_size"],
                            zero_init=False)
             return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K).reshape(shape)

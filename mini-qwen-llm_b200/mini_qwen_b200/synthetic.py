@@ -85,3 +85,50 @@ def zipf_router_bias(seed: int, E: int, s: float = 1.2, strength: float = 1.0) -
     bias = torch.empty(E, dtype=torch.float32)
     bias[order] = torch.tensor([-strength * s * math.log(r) for r in range(1, E + 1)], dtype=torch.float32)
     return bias
+
+
+# ---- W4A16 layers drawn directly on a device (whole 48-layer stacks: 15 GB of packed weights) -------------
+def gptq_zero_fix(qzeros: torch.Tensor) -> torch.Tensor:
+    """What ``LinearW4A16.from_gptq(..., zero_plus_one=True)`` does to the stored zero points
+    (mini_qwen/model/layers/linear_w4a16.py:96-99 of the reference): every nibble + 1, clamped to 15,
+    repacked.  Works on any device and shape."""
+    u = qzeros.to(torch.int64) & 0xFFFFFFFF
+    out = torch.zeros_like(u)
+    for i in range(8):
+        nib = torch.clamp(((u >> (4 * i)) & 0xF) + 1, max=15)
+        out |= nib << (4 * i)
+    out = torch.where(out >= 2 ** 31, out - 2 ** 32, out)
+    return out.to(torch.int32)
+
+
+def w4a16_stacks_on_device(device, seed: int, experts: int, H: int, I: int, group: int = 128):
+    """``experts`` experts of a W4A16 layer drawn on ``device`` with the distributions of the W4A16
+    configurations: int4 values uniform in [0, 15] (i.e. uniform packed words), fp16 scales uniform in
+    [0.005, 0.02] stored as bf16, stored zero points uniform in [0, 15] passed through the zero_plus_one
+    fix-up.  Returns (gate, up, down), each (qweight [E,K/8,N] int32, scales [E,K/g,N] bf16,
+    qzeros [E,K/g,N/8] int32) in the convention of the module buffers.  A pure function of (seed, shapes) on a
+    given device type."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+
+    def proj(kd, n):
+        qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (experts, kd // 8, n), generator=gen, device=device, dtype=torch.int32)
+        sc = (torch.rand(experts, kd // group, n, generator=gen, device=device) * 0.015 + 0.005)
+        sc = sc.to(torch.float16).to(torch.bfloat16)
+        qz = torch.randint(-2 ** 31, 2 ** 31 - 1, (experts, kd // group, n // 8), generator=gen, device=device,
+                           dtype=torch.int32)
+        return qw, sc, gptq_zero_fix(qz)
+    return proj(H, I), proj(H, I), proj(I, H)
+
+
+def router_weight_on_device(device, seed: int, E: int, H: int) -> torch.Tensor:
+    """Router weight ~N(0, 0.02) drawn as fp16 (the W4A16 configurations keep it in fp16) and held in bf16, as
+    the reference's GPTQ loader casts it (mini_qwen/model/loader.py:253-259)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    return (torch.randn(E, H, generator=gen, device=device) * 0.02).to(torch.float16).to(torch.bfloat16)
+
+
+def rms_norm_weightless(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """Weight-free RMS norm that keeps activations O(1) between chained MoE layers (the 48-layer stack has no
+    attention and no learnt norms; without it SwiGLU's quadratic growth overflows within a few layers)."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)

@@ -133,9 +133,14 @@ def w4_block_reference(lay, x, router_w, accumulate, bias=None):
     return out
 
 
-def w4_output_bar(out, ref, ref64):
+def w4_output_bar(out, ref, ref64, term_scale=None):
     """Output bar of the W4A16 block: rtol 2e-2 / atol 2e-3 against the reference's result, read the only
     way the reference itself can meet it.
+
+    ``term_scale`` ([T, 1] or None): magnitude of the bf16 terms an output element is a sum of, for inputs whose
+    outputs are not O(10-100) any more.  The absolute term then becomes 2e-3 * max(1, term_scale), i.e. half a
+    bf16 unit in the last place (2^-9) of those terms: a sum cannot be pinned more finely than the rounding of
+    what is summed.  None (every configuration of the benchmark proper) keeps the literal 2e-3.
 
     The quantised layer's outputs have magnitude 10-100 and are sums of bf16-rounded intermediates, so an
     element that nearly cancels carries the rounding of terms a thousand times larger: the reference
@@ -147,13 +152,14 @@ def w4_output_bar(out, ref, ref64):
       * no element is further from ``ref64`` than the literal bar or 1.5 x the largest |ref - ref64|.
     Returns (kernel share, reference share, kernel max distance, reference max distance)."""
     out, ref, ref64 = out.float(), ref.float(), ref64.float()
-    gpu_frac = ((out - ref).abs() > ATOL + RTOL * ref.abs()).float().mean().item()
-    ref_frac = ((ref - ref64).abs() > ATOL + RTOL * ref64.abs()).float().mean().item()
+    atol = ATOL if term_scale is None else ATOL * term_scale.float().clamp(min=1.0)
+    gpu_frac = ((out - ref).abs() > atol + RTOL * ref.abs()).float().mean().item()
+    ref_frac = ((ref - ref64).abs() > atol + RTOL * ref64.abs()).float().mean().item()
     gpu_dist = (out - ref64).abs()
     ref_dist = (ref - ref64).abs().max().item()
     assert gpu_frac <= 2 * ref_frac + 1e-4, (
         f"{gpu_frac:.4%} of the kernel's elements outside rtol/atol; the reference's own share is {ref_frac:.4%}")
-    allowed = torch.maximum(ATOL + RTOL * ref64.abs(), torch.full_like(ref64, 1.5 * ref_dist))
+    allowed = torch.maximum(atol + RTOL * ref64.abs(), torch.full_like(ref64, 1.5 * ref_dist))
     worst = (gpu_dist - allowed).max().item()
     assert worst <= 0, f"an element is {worst:.4g} further from the exact-sum result than allowed"
     return gpu_frac, ref_frac, gpu_dist.max().item(), ref_dist

@@ -118,6 +118,11 @@ def test_block_config3_w4a16_decode(T):
               f"max distance from exact sums {shares[2]:.4g} (reference {shares[3]:.4g})")
         assert torch.equal(blk(x), got)                     # deterministic across calls
     blk.w4_kernel = "stream"
+    # routing by the separate kernels instead of the fused small-batch launch: the same experts; the weights
+    # come from logits summed in another order, so the outputs agree to the bar, not to the bit
+    blk.fuse_small_batches = False
+    cases.w4_output_bar(cpu(blk(x)), ref, ref64)
+    blk.fuse_small_batches = True
     blk.check_status()
 
 
@@ -217,7 +222,8 @@ def test_block_forward_captured_in_a_cuda_graph(w4):
         blk, x = dense_block(lay), lay.x.to(DEV)
     eager = blk(x).clone()
     cap = CapturedForward(blk, x)
-    assert cap.launches >= 5
+    # W4A16 at 16 tokens: fused routing, gate/up, down, combine; dense: router (2), plan (3), gate/up, down, combine
+    assert cap.launches == (4 if w4 else 8)
     assert torch.equal(cap.replay(), eager)
     x2 = torch.roll(x, 3, dims=0).contiguous()
     cap.x.copy_(x2)

@@ -337,3 +337,42 @@ def test_w4a16_zero_point_extremes():
     x = torch.ones(3, K, dtype=torch.bfloat16)
     out = w4a16_gemm(x.to(DEV), qw.to(DEV), sc.to(DEV), qz.to(DEV), gs)
     assert torch.equal(cpu(out), O.w4a16_linear(x, qw, sc, qz, gs))
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("T,E,K,H,dtype,renorm,biased", [
+    (1, 128, 8, 2048, torch.bfloat16, True, False), (8, 128, 8, 2048, torch.bfloat16, True, False),
+    (16, 128, 8, 2048, torch.float16, False, False), (64, 128, 8, 2048, torch.bfloat16, True, True),
+    (5, 16, 4, 256, torch.float32, True, False), (33, 256, 8, 512, torch.bfloat16, False, True),
+    (64, 8, 2, 136, torch.float32, True, False)])
+def test_fused_small_batch_routing_equals_the_separate_kernels_and_the_oracle(T, E, K, H, dtype, renorm, biased):
+    """mq_route_small (logits + top-k + plan + preparation in one launch) against the CPU oracle (ids, plan
+    bit-exact) and against the separate launches it replaces."""
+    from mini_qwen_b200.kernels.moe_router import moe_route_small, route_small_workspace
+    from mini_qwen_b200.kernels.w4a16_gemm import w4a16_tc_prep
+    g = torch.Generator().manual_seed(T * 1000 + E)
+    x = torch.randn(T, H, generator=g).to(dtype)
+    w = (torch.randn(E, H, generator=g) * 0.02).to(dtype)
+    bias = (torch.randn(E, generator=g) * 0.5) if biased else None
+    prepare = dtype == torch.bfloat16 and H % 128 == 0
+    ws = route_small_workspace(E, DEV)
+    for _ in range(2):                                   # the second call finds the workspace as the first left it
+        ids32, wts, perm, inv, off32, xp, xs = moe_route_small(
+            x.to(DEV), w.to(DEV), K, bias=None if bias is None else bias.to(DEV), renormalize=renorm,
+            prepare=prepare, workspace=ws)
+        ref_ids, ref_w = O.router(x, w, K, bias)
+        if renorm:
+            ref_w = O.renormalise(ref_w)
+        assert torch.equal(cpu(ids32).to(torch.int64), ref_ids)
+        torch.testing.assert_close(cpu(wts), ref_w, rtol=1e-4, atol=1e-6)
+        ref_perm, ref_inv = O.sort_slots(ref_ids)
+        assert torch.equal(cpu(perm).to(torch.int64), ref_perm) and torch.equal(cpu(inv).to(torch.int64), ref_inv)
+        assert torch.equal(cpu(off32).to(torch.int64), O.expert_offsets(ref_ids, E))
+        if prepare:
+            xp2, xs2 = w4a16_tc_prep(x.to(DEV))          # per token, no gather
+            assert torch.equal(xp, xp2) and torch.equal(xs[:, : H // 128], xs2[:, : H // 128])
+    # the separate launches give the same weights bit for bit or within an fp32 rounding of the logits
+    ids_b, w_b, ids32_b = moe_router(x.to(DEV), w.to(DEV), K, bias=None if bias is None else bias.to(DEV),
+                                     renormalize=renorm, return_int32_ids=True)
+    assert torch.equal(ids32_b, ids32)
+    torch.testing.assert_close(w_b, wts, rtol=1e-5, atol=1e-7)
