@@ -145,6 +145,25 @@ int mq_unpermute_combine(const void* rows, int dtype, const float* weights, cons
                          int64_t T, int64_t K, int64_t H, void* out, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * The decoder layer's glue either side of the block (mini_qwen/model/qwen3_moe.py:63-66:
+ * h + mlp(post_attention_layernorm(h))).
+ * mq_rms_norm replaces RMSNorm.forward (mini_qwen/model/layers/rms_norm.py:11-18) on [T,H] rows:
+ *   out = weight * cast(float(x) * 1/sqrt(mean(float(x)^2) + eps)), the mean, the root and the
+ *   reciprocal correctly rounded in fp32, the cast to `dtype` before the product with weight [H].
+ *   Row sums run in a different order from the reference's CPU sum, so values can differ from it by
+ *   one unit in the last place of `dtype`.
+ * mq_unpermute_combine_residual is mq_unpermute_combine followed by the layer's residual add in the
+ *   same kernel: out[t,:] = cast(float(residual[t,:]) + float(cast(sum_k ...))), the block output
+ *   rounded to `dtype` before the add as the reference's two separate tensors are.  residual [T,H]
+ *   of `dtype`, 16-byte aligned; NULL gives mq_unpermute_combine.  out may alias residual.
+ */
+int mq_rms_norm(const void* x, int dtype, const void* weight, float eps, int64_t T, int64_t H,
+                void* out, void* stream);
+int mq_unpermute_combine_residual(const void* rows, int dtype, const float* weights, const int32_t* inv,
+                                  const void* residual, int64_t T, int64_t K, int64_t H, void* out,
+                                  void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Grouped GEMM, one projection.  Replaces moe_grouped_gemm / _moe_grouped_gemm_oracle
  * (mini_qwen/kernels/moe_grouped_gemm.py:17-37,115-156): for every expert e,
  * out[off[e]:off[e+1], :] = a[off[e]:off[e+1], :] . w[e]^T with fp32 accumulation.
@@ -313,7 +332,9 @@ int mq_w4a16_tc_swiglu(const void* xp, const float* xs,
  *   output buffers) deliver the slot's output row to row p of this rank's buffer, after which the
  *   source finishes with a local mq_unpermute_combine instead of mq_ep_combine.
  * mq_ep_combine: fused combine + unpermute.  out[t,:] = cast(sum_k weights[t,k] *
- *   float(y_owner[slot_dst[inv[t*K+k]]])), fp32 multiply then add, k ascending.
+ *   float(y_owner[slot_dst[inv[t*K+k]]])), fp32 multiply then add, k ascending.  residual
+ *   (optional, [T,H] of `dtype`): the layer's residual add in the same kernel, as in
+ *   mq_unpermute_combine_residual.
  */
 int mq_ep_share_counts(const int32_t* offsets, int64_t E, int64_t G, int64_t rank,
                        const uint64_t* peer_counts_ptrs, void* stream);
@@ -352,8 +373,8 @@ int mq_ep_dispatch_unique(const void* x, int dtype, const int32_t* uniq, const i
                           const uint64_t* peer_home_ptrs, int64_t cap_rows, int32_t* slot_dst,
                           int32_t* d_status, void* stream);
 int mq_ep_combine(const uint64_t* peer_y_ptrs, int dtype, const float* weights, const int32_t* inv,
-                  const int32_t* slot_dst, int64_t T, int64_t K, int64_t H, int64_t cap_rows,
-                  void* out, void* stream);
+                  const int32_t* slot_dst, const void* residual, int64_t T, int64_t K, int64_t H,
+                  int64_t cap_rows, void* out, void* stream);
 
 #ifdef __cplusplus
 }

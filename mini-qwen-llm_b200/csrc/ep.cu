@@ -375,8 +375,8 @@ ep_dispatch_unique_kernel(const uint4* __restrict__ x, const int32_t* __restrict
 template <typename T>
 __global__ void __launch_bounds__(128)
 ep_combine_kernel(const uint64_t* __restrict__ peer_y, const float* __restrict__ weights,
-                  const int32_t* __restrict__ inv, const int32_t* __restrict__ slot_dst, int K, int64_t H,
-                  int64_t cap_rows, T* __restrict__ out) {
+                  const int32_t* __restrict__ inv, const int32_t* __restrict__ slot_dst,
+                  const T* __restrict__ residual, int K, int64_t H, int64_t cap_rows, T* __restrict__ out) {
   __shared__ const T* s_row[32];
   __shared__ float s_w[32];
   const int64_t t = blockIdx.x;
@@ -418,15 +418,24 @@ ep_combine_kernel(const uint64_t* __restrict__ peer_y, const float* __restrict__
   T o[V];
 #pragma unroll
   for (int j = 0; j < V; ++j) o[j] = from_float<T>(acc[j]);
+  if (residual) {
+    // the decoder layer's add of two model-type tensors: the block output is rounded first
+    const uint4 rraw = *reinterpret_cast<const uint4*>(residual + t * H + h0);
+    const T* rv = reinterpret_cast<const T*>(&rraw);
+#pragma unroll
+    for (int j = 0; j < V; ++j) o[j] = from_float<T>(__fadd_rn(to_float<T>(rv[j]), to_float<T>(o[j])));
+  }
   *reinterpret_cast<uint4*>(out + t * H + h0) = *reinterpret_cast<const uint4*>(o);
 }
 
 template <typename T>
 int launch_ep_combine(const uint64_t* peer_y, const float* weights, const int32_t* inv, const int32_t* slot_dst,
-                      int64_t T_, int K, int64_t H, int64_t cap_rows, void* out, cudaStream_t st) {
+                      const void* residual, int64_t T_, int K, int64_t H, int64_t cap_rows, void* out,
+                      cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
   dim3 grid((unsigned)T_, (unsigned)((H + 128 * V - 1) / (128 * V)));
-  ep_combine_kernel<T><<<grid, 128, 0, st>>>(peer_y, weights, inv, slot_dst, K, H, cap_rows, reinterpret_cast<T*>(out));
+  ep_combine_kernel<T><<<grid, 128, 0, st>>>(peer_y, weights, inv, slot_dst, reinterpret_cast<const T*>(residual), K, H,
+                                            cap_rows, reinterpret_cast<T*>(out));
   return check_launch();
 }
 
@@ -484,17 +493,20 @@ extern "C" int mq_ep_dispatch(const void* x, int dtype, const int32_t* perm, con
 }
 
 extern "C" int mq_ep_combine(const uint64_t* peer_y_ptrs, int dtype, const float* weights, const int32_t* inv,
-                             const int32_t* slot_dst, int64_t T, int64_t K, int64_t H, int64_t cap_rows,
-                             void* out, void* stream) {
+                             const int32_t* slot_dst, const void* residual, int64_t T, int64_t K, int64_t H,
+                             int64_t cap_rows, void* out, void* stream) {
   using namespace mq;
   if (T < 0 || K <= 0 || H <= 0 || cap_rows <= 0 || !valid_dtype(dtype)) return MQ_ERR_INVALID_ARGUMENT;
   if (K > 32 || (H * (int64_t)dtype_size(dtype)) % 16 != 0) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (T == 0) return MQ_OK;
-  if (!peer_y_ptrs || !weights || !inv || !slot_dst || !out || !aligned16(out)) return MQ_ERR_INVALID_ARGUMENT;
+  if (!peer_y_ptrs || !weights || !inv || !slot_dst || !out || !aligned16(out) || !aligned16(residual))
+    return MQ_ERR_INVALID_ARGUMENT;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == MQ_F32) return launch_ep_combine<float>(peer_y_ptrs, weights, inv, slot_dst, T, (int)K, H, cap_rows, out, st);
-  if (dtype == MQ_BF16) return launch_ep_combine<__nv_bfloat16>(peer_y_ptrs, weights, inv, slot_dst, T, (int)K, H, cap_rows, out, st);
-  return launch_ep_combine<__half>(peer_y_ptrs, weights, inv, slot_dst, T, (int)K, H, cap_rows, out, st);
+  if (dtype == MQ_F32)
+    return launch_ep_combine<float>(peer_y_ptrs, weights, inv, slot_dst, residual, T, (int)K, H, cap_rows, out, st);
+  if (dtype == MQ_BF16)
+    return launch_ep_combine<__nv_bfloat16>(peer_y_ptrs, weights, inv, slot_dst, residual, T, (int)K, H, cap_rows, out, st);
+  return launch_ep_combine<__half>(peer_y_ptrs, weights, inv, slot_dst, residual, T, (int)K, H, cap_rows, out, st);
 }
 
 extern "C" int mq_ep_unique_rows(const int32_t* topk_ids, int64_t T, int64_t K, int64_t E, int64_t G,

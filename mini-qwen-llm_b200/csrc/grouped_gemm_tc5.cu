@@ -95,6 +95,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
+// Untiled bulk store of `bytes` contiguous bytes from shared memory (both addresses 16-byte aligned); the
+// destination may be another GPU's memory (a plain store, nothing is read from the peer).
+__device__ __forceinline__ void bulk_store_1d(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the stores issued by this thread have finished READING their shared-memory source
+__device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
 }
@@ -451,7 +461,12 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     const int wig = (warp - 2) & 3;                // warp within the group: stores rows 8*wig .. 8*wig+7
     uint8_t* stg = bar_mem + 256 + half * STG_BYTES;
     volatile int* group_go = reinterpret_cast<volatile int*>(bar_mem + 8 * (2 * NST + 4) + 16) + half;
-    const int pitch = cols_per_tile * 2;
+    // Rows that are scattered (expert parallelism: each goes to the GPU and row its code names) leave by bulk
+    // stores, one 256-byte row per elected lane: the copy engine moves them while the warps go on, and a peer
+    // receives whole rows instead of 16-byte pieces.  A bulk store reads its row as it lies in shared memory, so
+    // the staging rows are then unswizzled and padded by 16 bytes instead (272-byte pitch: conflict-free too).
+    const bool bulk_rows = DOUBLE && row_dst != nullptr;
+    const int pitch = bulk_rows ? cols_per_tile * 2 + 16 : cols_per_tile * 2;
     Tile tl;
     int it = 0;
     for (int t = blockIdx.x;; t += gridDim.x, ++it) {
@@ -500,7 +515,7 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
             for (int j2 = 0; j2 < 2; ++j2) {
               const int tok = 8 * (2 * j2 + (mi >> 1)) + ri;                       // token row of the chunk
               const int piece = (sub2 * TM + quad * 32 + 16 * hl + 8 * (mi & 1)) >> 3;   // 16-byte piece of the row
-              const uint32_t addr = stg_s + tok * pitch + ((piece ^ (tok & 7)) << 4);
+              const uint32_t addr = stg_s + tok * pitch + ((bulk_rows ? piece : (piece ^ (tok & 7))) << 4);
               stmatrix_x4_trans(addr, m[2 * j2][0], m[2 * j2][1], m[2 * j2 + 1][0], m[2 * j2 + 1][1]);
             }
           }
@@ -522,7 +537,21 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
           }
         }
         epi_group_sync(half);                          // the chunk's rows are complete
-        if (SWIGLU || DOUBLE) {
+        if (bulk_rows) {
+          // lanes 0-7 of each warp send one row each; everyone waits until the copy engine has read them
+          if (lane < 8) {
+            const int row = 8 * wig + lane;
+            if (row < valid) {
+              const int code = row_dst[(int64_t)tl.tok0 + c + row];
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(dst_bases[code >> ROW_BITS]) +
+                                   (size_t)(code & ROW_MASK) * N + f0;
+              fence_proxy_async();                       // the staged rows (generic proxy) before the copy engine reads them
+              bulk_store_1d(dst, stg_s + row * pitch, (uint32_t)(cols_per_tile * 2));
+            }
+            bulk_store_commit();
+            bulk_store_wait_read();
+          }
+        } else if (SWIGLU || DOUBLE) {
           // 16 lanes cover a 256-byte row: two rows per instruction
           const int piece = lane & 15;
 #pragma unroll

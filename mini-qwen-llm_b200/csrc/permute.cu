@@ -141,10 +141,19 @@ gather_rows_bytes(const uint8_t* __restrict__ x, const int32_t* __restrict__ per
 // ---------------------------------------------------------------------------------------------
 // out[t,h] = cast( sum_k w[t,k] * float(rows[inv[t*K+k], h]) ): the product is rounded to fp32
 // before the add (no FMA contraction), k ascending, as a tensor multiply followed by sum(dim=1).
+// With `residual` the decoder layer's add follows (mini_qwen/model/qwen3_moe.py:66): the block output is
+// first rounded to the model type, then out = cast(float(residual) + float(block output)).
+template <typename T>
+__device__ __forceinline__ T finish_combine(float acc, const T* residual, int64_t at) {
+  const T o = from_float<T>(acc);
+  return residual ? from_float<T>(__fadd_rn(to_float<T>(residual[at]), to_float<T>(o))) : o;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 unpermute_combine(const T* __restrict__ rows, const float* __restrict__ weights,
-                  const int32_t* __restrict__ inv, int K, int64_t H, T* __restrict__ out) {
+                  const int32_t* __restrict__ inv, const T* __restrict__ residual, int K, int64_t H,
+                  T* __restrict__ out) {
   __shared__ int s_row[32];
   __shared__ float s_w[32];
   const int64_t t = blockIdx.x;
@@ -168,26 +177,33 @@ unpermute_combine(const T* __restrict__ rows, const float* __restrict__ weights,
       for (int j = 0; j < V; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(wk, to_float<T>(v[j])));
     }
     T o[V];
+    if (residual) {
+      const uint4 rraw = *reinterpret_cast<const uint4*>(residual + t * H + h0);
+      const T* rv = reinterpret_cast<const T*>(&rraw);
 #pragma unroll
-    for (int j = 0; j < V; ++j) o[j] = from_float<T>(acc[j]);
+      for (int j = 0; j < V; ++j) o[j] = finish_combine<T>(acc[j], rv, j);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = from_float<T>(acc[j]);
+    }
     *reinterpret_cast<uint4*>(out + t * H + h0) = *reinterpret_cast<const uint4*>(o);
   } else {
     for (int j = 0; j < V && h0 + j < H; ++j) {
       float a = 0.0f;
       for (int k = 0; k < K; ++k)
         a = __fadd_rn(a, __fmul_rn(s_w[k], to_float<T>(rows[(int64_t)s_row[k] * H + h0 + j])));
-      out[t * H + h0 + j] = from_float<T>(a);
+      out[t * H + h0 + j] = finish_combine<T>(a, residual, t * H + h0 + j);
     }
   }
 }
 
 template <typename T>
-int launch_combine(const void* rows, const float* weights, const int32_t* inv, int64_t T_, int K, int64_t H,
-                   void* out, cudaStream_t st) {
+int launch_combine(const void* rows, const float* weights, const int32_t* inv, const void* residual, int64_t T_,
+                   int K, int64_t H, void* out, cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
   dim3 grid((unsigned)T_, (unsigned)((H + 128 * V - 1) / (128 * V)));
-  unpermute_combine<T><<<grid, 128, 0, st>>>(reinterpret_cast<const T*>(rows), weights, inv, K, H,
-                                            reinterpret_cast<T*>(out));
+  unpermute_combine<T><<<grid, 128, 0, st>>>(reinterpret_cast<const T*>(rows), weights, inv,
+                                            reinterpret_cast<const T*>(residual), K, H, reinterpret_cast<T*>(out));
   return check_launch();
 }
 
@@ -250,16 +266,22 @@ extern "C" int mq_gather_rows(const void* x, int dtype, const int32_t* perm, int
   return check_launch();
 }
 
-extern "C" int mq_unpermute_combine(const void* rows, int dtype, const float* weights, const int32_t* inv,
-                                    int64_t T, int64_t K, int64_t H, void* out, void* stream) {
+extern "C" int mq_unpermute_combine_residual(const void* rows, int dtype, const float* weights, const int32_t* inv,
+                                             const void* residual, int64_t T, int64_t K, int64_t H, void* out,
+                                             void* stream) {
   using namespace mq;
   if (T < 0 || K <= 0 || H <= 0 || !valid_dtype(dtype)) return MQ_ERR_INVALID_ARGUMENT;
   if (K > 32) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (T == 0) return MQ_OK;
   if (!rows || !weights || !inv || !out) return MQ_ERR_INVALID_ARGUMENT;
-  if (!aligned16(rows) || !aligned16(out)) return MQ_ERR_INVALID_ARGUMENT;
+  if (!aligned16(rows) || !aligned16(out) || !aligned16(residual)) return MQ_ERR_INVALID_ARGUMENT;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == MQ_F32) return launch_combine<float>(rows, weights, inv, T, (int)K, H, out, st);
-  if (dtype == MQ_BF16) return launch_combine<__nv_bfloat16>(rows, weights, inv, T, (int)K, H, out, st);
-  return launch_combine<__half>(rows, weights, inv, T, (int)K, H, out, st);
+  if (dtype == MQ_F32) return launch_combine<float>(rows, weights, inv, residual, T, (int)K, H, out, st);
+  if (dtype == MQ_BF16) return launch_combine<__nv_bfloat16>(rows, weights, inv, residual, T, (int)K, H, out, st);
+  return launch_combine<__half>(rows, weights, inv, residual, T, (int)K, H, out, st);
+}
+
+extern "C" int mq_unpermute_combine(const void* rows, int dtype, const float* weights, const int32_t* inv,
+                                    int64_t T, int64_t K, int64_t H, void* out, void* stream) {
+  return mq_unpermute_combine_residual(rows, dtype, weights, inv, nullptr, T, K, H, out, stream);
 }

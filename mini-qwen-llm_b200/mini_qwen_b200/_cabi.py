@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
 import torch
@@ -32,6 +32,8 @@ PROTOTYPES = {
     "mq_permute_plan": (c_int, [_P, _I, _L, _L, _L, _P, _P, _P, _P, _P, c_size_t, _P]),
     "mq_gather_rows": (c_int, [_P, _I, _P, _L, _L, _L, _P, _P]),
     "mq_unpermute_combine": (c_int, [_P, _I, _P, _P, _L, _L, _L, _P, _P]),
+    "mq_unpermute_combine_residual": (c_int, [_P, _I, _P, _P, _P, _L, _L, _L, _P, _P]),
+    "mq_rms_norm": (c_int, [_P, _I, _P, c_float, _L, _L, _P, _P]),
     "mq_grouped_gemm": (c_int, [_P, _P, _P, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
     "mq_grouped_swiglu": (c_int, [_P, _P, _P, _L, _L, _L, _L, _L, _I, _P, _P, _P]),
     "mq_grouped_gemm_scatter": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _I, _P, _P]),
@@ -51,7 +53,7 @@ PROTOTYPES = {
     "mq_ep_dispatch": (c_int, [_P, _I, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _P, _L, _P, _P, _P]),
     "mq_ep_unique_rows": (c_int, [_P, _L, _L, _L, _L, _P, _P]),
     "mq_ep_dispatch_unique": (c_int, [_P, _I, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _P, _P, _P, _L, _P, _P, _P]),
-    "mq_ep_combine": (c_int, [_P, _I, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
+    "mq_ep_combine": (c_int, [_P, _I, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
 }
 
 _lib = None

@@ -20,6 +20,7 @@ from ...kernels.moe_grouped_gemm import (gather_swiglu_supported, moe_grouped_ge
 from ...kernels.moe_permute import gather_rows, moe_permute_plan
 from ...kernels.moe_router import moe_route_small, moe_router, route_small_supported, route_small_workspace
 from ...kernels.moe_unpermute import unpermute_combine
+from .rms_norm import RMSNorm
 from ...kernels.w4a16_gemm import (w4a16_grouped_gemm, w4a16_grouped_swiglu, w4a16_stream_supported,
                                      w4a16_stream_swiglu, w4a16_tc_gemm, w4a16_tc_prep, w4a16_tc_supported,
                                      w4a16_tc_swiglu)
@@ -221,12 +222,19 @@ class Qwen3MoEBlock(nn.Module):
         return self._stacks
 
     # ------------------------------------------------------------------ forward
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """The block on ``x`` [..., H].  With ``residual`` (same shape and dtype) the result is
+        ``residual + block(x)``, the add done by the combine kernel as an add of two model-dtype tensors."""
         shape = x.shape
         x2d = x.reshape(-1, shape[-1])
         if not x2d.is_contiguous():
             x2d = x2d.contiguous()
         T = x2d.shape[0]
+        res = None
+        if residual is not None:
+            if residual.shape != x.shape or residual.dtype != x.dtype:
+                raise ValueError("residual must have the shape and dtype of the block's input")
+            res = residual.reshape(-1, shape[-1]).contiguous()
         K, E = self.num_experts_per_tok, self.num_experts
         st = self._ready()
 
@@ -246,13 +254,13 @@ class Qwen3MoEBlock(nn.Module):
                                     renormalize=self.norm_topk_prob, return_int32_ids=True)
             perm, inv, off32, _ = run("permute_plan", moe_permute_plan, ids32, E, want_int64_offsets=False)
         if self.ep_size > 1 and self.ep_mode == "p2p":
-            return self._forward_peer(x2d, st, weights, ids32, perm, inv, off32, T, K, E).reshape(shape)
+            return self._forward_peer(x2d, st, weights, ids32, perm, inv, off32, T, K, E, res).reshape(shape)
         if self.ep_size == 1 and not st["w4"] and gather_swiglu_supported(x2d, st["w13"]):
             # the gate/up kernel fetches the rows through the permutation itself: no permuted copy
             status = self._status_word(x2d.device)
             h = run("grouped_swiglu", moe_grouped_swiglu_gather, x2d, perm, K, st["w13"], off32, status=status)
             out_perm = run("grouped_down", moe_grouped_gemm, h, st["w2"], off32, zero_init=False, status=status)
-            return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K).reshape(shape)
+            return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K, residual=res).reshape(shape)
         if self.ep_size == 1 and st["w4"] and self._w4_stream(st):
             # decode path: one preparation launch replaces the row gather, the gate/up kernel then needs no byte
             # permutes and no extra MMAs for the group sums
@@ -267,13 +275,13 @@ class Qwen3MoEBlock(nn.Module):
                         st["group_size"], shuffle_out=False, status=status)
             out_perm = run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off32, st["group_size"],
                            zero_init=False)
-            return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K).reshape(shape)
+            return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K, residual=res).reshape(shape)
         if self.ep_size == 1 and st["w4"] and self._w4_tc(st, T * K):
             # decode-size groups: weights dequantised into tensor memory, activations prepared once
             status = self._status_word(x2d.device)
             xp, xs = run("w4_prep", w4a16_tc_prep, x2d, perm, K)
             out_perm = self._experts_w4_tc(st, xp, xs, off32, status)
-            return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K).reshape(shape)
+            return run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K, residual=res).reshape(shape)
         plan = None
         if self.ep_size > 1:
             all_counts = parallel.gather_counts(off32[1:] - off32[:-1], self.ep_group)
@@ -285,8 +293,13 @@ class Qwen3MoEBlock(nn.Module):
         out_perm = self._experts(st, permuted, off32)
         if plan is not None:
             out_perm = run("combine", parallel.combine, out_perm, plan, self.ep_group)
-        out = run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K)
+        out = run("unpermute_combine", unpermute_combine, out_perm, weights, inv, T, K, residual=res)
         return out.reshape(shape)
+
+    def half_layer(self, h: torch.Tensor, norm: "RMSNorm") -> torch.Tensor:
+        """Second half of the reference's MoE decoder layer (``mini_qwen/model/qwen3_moe.py:63-66``):
+        ``h + self(norm(h))`` with ``norm`` the layer's post-attention RMSNorm; the add runs in the combine kernel."""
+        return self.forward(norm(h), residual=h)
 
     def _experts(self, st, rows, off32, out=None):
         """Grouped gate/up + SwiGLU and down projection over rows grouped by `off32`."""
@@ -342,7 +355,7 @@ class Qwen3MoEBlock(nn.Module):
         if self._peer is not None:
             self._peer.check_status()
 
-    def _forward_peer(self, x2d, st, weights, ids32, perm, inv, off32, T, K, E):
+    def _forward_peer(self, x2d, st, weights, ids32, perm, inv, off32, T, K, E, res=None):
         """Expert-parallel path over peer memory: rows go straight from x into the owners' receive
         buffers and expert outputs are read straight from the owners while combining."""
         run = self._stage
@@ -381,13 +394,14 @@ class Qwen3MoEBlock(nn.Module):
                     status=status)
                 run("rank_barrier", peer.rank_barrier)
                 # every row of this rank's sorted order is back in its own buffer
-                return run("unpermute_combine", unpermute_combine, peer.y_rows()[:T * K], weights, inv, T, K)
+                return run("unpermute_combine", unpermute_combine, peer.y_rows()[:T * K], weights, inv, T, K,
+                           residual=res)
             run("grouped_down", moe_grouped_gemm, h, st["w2"], seg, zero_init=False, out=peer.y_rows(), status=status)
             run("rank_barrier", peer.rank_barrier)
-            return run("combine", peer.combine, weights, inv, slot_dst, T, K)
+            return run("combine", peer.combine, weights, inv, slot_dst, T, K, residual=res)
         self._experts(st, peer.recv_rows(), seg, out=peer.y_rows())
         run("rank_barrier", peer.rank_barrier)
-        return run("combine", peer.combine, weights, inv, slot_dst, T, K)
+        return run("combine", peer.combine, weights, inv, slot_dst, T, K, residual=res)
 
     def _stage(self, name, fn, *args, **kwargs):
         """Runs one stage; with ``kernel_events`` set, brackets it with CUDA events on the current stream."""

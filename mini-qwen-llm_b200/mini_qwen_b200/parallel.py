@@ -266,12 +266,14 @@ class PeerExchange:
         c.count_launches(2 if T else 0)
         return slot_dst
 
-    def combine(self, weights, inv, slot_dst, num_tokens: int, top_k: int) -> torch.Tensor:
-        """Fused combine + unpermute from the owners' output buffers."""
+    def combine(self, weights, inv, slot_dst, num_tokens: int, top_k: int, residual=None) -> torch.Tensor:
+        """Fused combine + unpermute from the owners' output buffers (plus the layer's residual add, if given)."""
         c = self._cabi
         out = torch.empty(num_tokens, self.hidden, dtype=self.dtype, device=weights.device)
+        if residual is not None:
+            assert residual.shape == out.shape and residual.dtype == out.dtype and residual.is_contiguous()
         rc = c.load().mq_ep_combine(c.ptr(self.y_ptrs), c.dtype_code(out), c.ptr(weights), c.ptr(inv), c.ptr(slot_dst),
-                                    num_tokens, top_k, self.hidden, self.cap_rows, c.ptr(out),
+                                    c.ptr(residual), num_tokens, top_k, self.hidden, self.cap_rows, c.ptr(out),
                                     c.stream_ptr(weights.device))
         c.check(rc, "mq_ep_combine")
         c.count_launches(1 if num_tokens else 0)

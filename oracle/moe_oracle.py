@@ -136,6 +136,24 @@ def block_forward(x, gate_w, w_gate, w_up, w_down, top_k: int, norm_topk_prob: b
     return out.reshape(shape), ids, wts, off
 
 
+# --------------------------------------------------------------------------- decoder-layer glue
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """RMSNorm as the reference computes it (mini_qwen/model/layers/rms_norm.py:11-18): normalise in fp32,
+    cast back to the input dtype, THEN multiply by the weight (a product of two tensors of the model dtype)."""
+    xf = x.float()
+    rms = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return weight * (xf * rms).to(x.dtype)
+
+
+def moe_half_layer(h, norm_weight, eps, gate_w, w_gate, w_up, w_down, top_k: int, norm_topk_prob: bool = True,
+                   bias=None, expert_fn=None):
+    """Second half of the reference's MoE decoder layer (mini_qwen/model/qwen3_moe.py:63-66):
+    ``h + mlp(post_attention_layernorm(h))``.  Returns (out, normalised input, ids)."""
+    xn = rms_norm(h, norm_weight, eps)
+    out, ids, _, _ = block_forward(xn, gate_w, w_gate, w_up, w_down, top_k, norm_topk_prob, bias, expert_fn)
+    return h + out, xn, ids
+
+
 # --------------------------------------------------------------------------- int4 format
 def pack_int4(x: torch.Tensor) -> torch.Tensor:
     """8 values of 4 bits -> one int32 along the last axis, value i in bits [4i, 4i+4)

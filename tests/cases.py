@@ -75,6 +75,24 @@ def w4_gemm_inputs(M, K, N):
     return x, w
 
 
+# ---- decoder-layer glue around the block: post-attention RMSNorm in, residual add out --------------------
+# (reference: mini_qwen/model/qwen3_moe.py:63-66 with mini_qwen/model/layers/rms_norm.py:11-18)
+GLUE_CASES = [
+    dict(seed=61, T=64, H=256, E=8, K=2, I=512, dtype=torch.float32, eps=1e-6),
+    dict(seed=62, T=40, H=256, E=16, K=4, I=128, dtype=torch.bfloat16, eps=1e-6),
+    dict(seed=63, T=3, H=512, E=16, K=4, I=256, dtype=torch.bfloat16, eps=1e-5),
+]
+
+
+def glue_case_inputs(c):
+    """(layer, hidden states h [T,H] ~N(0,2) with a per-row scale, norm weight ~N(1,0.1)) of a glue case."""
+    lay = synthetic.dense_layer(c["seed"], c["T"], c["H"], c["E"], c["K"], c["I"], c["dtype"])
+    g = torch.Generator().manual_seed(c["seed"] + 1000)
+    h = (torch.randn(c["T"], c["H"], generator=g) * (0.5 + 3.0 * torch.rand(c["T"], 1, generator=g))).to(c["dtype"])
+    norm_w = (1.0 + 0.1 * torch.randn(c["H"], generator=g)).to(c["dtype"])
+    return lay, h, norm_w
+
+
 # ---- benchmark configurations ------------------------------------------------------------------
 @functools.lru_cache(maxsize=1)
 def config1():

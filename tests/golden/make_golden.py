@@ -195,6 +195,25 @@ def main():
         np.savez_compressed(os.path.join(HERE, "quant_cases.npz"), **rec)
         print("quant_cases done")
 
+    if want("glue"):
+        # post-attention RMSNorm -> MoE block -> residual add, as the reference's decoder layer does it
+        import mini_qwen.model.layers.rms_norm as r_norm
+        rec = {}
+        for i, c in enumerate(cases.GLUE_CASES):
+            lay, h, norm_w = cases.glue_case_inputs(c)
+            cfg = SimpleNamespace(hidden_size=c["H"], intermediate_size=c["I"], num_experts=c["E"],
+                                  num_experts_per_tok=c["K"], norm_topk_prob=True)
+            blk = ref_block(ref, cfg, lay.router, lay.gate, lay.up, lay.down, c["dtype"])
+            norm = r_norm.RMSNorm(c["H"], eps=c["eps"]).to(c["dtype"])
+            norm.weight.data = norm_w.clone()
+            with torch.no_grad():
+                xn = norm(h)
+                ids, _ = r_router.moe_router(xn, lay.router, c["K"])
+                out = h + blk(xn)
+            rec[f"normed_{i}"], rec[f"ids_{i}"], rec[f"out_{i}"] = bits(xn), ids.numpy(), bits(out)
+        np.savez_compressed(os.path.join(HERE, "glue_cases.npz"), **rec)
+        print("glue_cases done")
+
     if want("c1"):
         run_dense(ref, "c1", cases.config1())
         print("c1 done")

@@ -7,7 +7,7 @@ import torch
 import cases
 from mini_qwen_b200 import Qwen3MoEConfig
 from mini_qwen_b200.kernels import moe_permute_plan, moe_router
-from mini_qwen_b200.model.layers import LinearW4A16, Qwen3MoEBlock
+from mini_qwen_b200.model.layers import LinearW4A16, Qwen3MoEBlock, RMSNorm, rms_norm
 from oracle import moe_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -229,3 +229,62 @@ def test_block_forward_captured_in_a_cuda_graph(w4):
     cap.x.copy_(x2)
     assert torch.equal(cap.replay(), blk(x2))
     blk.check_status()
+
+
+@pytest.mark.parametrize("i", range(len(cases.GLUE_CASES)))
+def test_decoder_layer_glue(i):
+    """RMSNorm in, residual add out (reference: model/qwen3_moe.py:63-66).  The norm's row sums run in another
+    order than the reference's CPU sum, so a normalised value may sit one unit in the last place away; rows whose
+    normalised values are bit-identical must then route identically and meet the block's output bar against the
+    stored reference output, and every row must meet it against the oracle fed with the GPU's own normalised rows."""
+    c = cases.GLUE_CASES[i]
+    g = cases.golden("glue_cases")
+    lay, h, norm_w = cases.glue_case_inputs(c)
+    dt = c["dtype"]
+    blk = dense_block(lay)
+    norm = RMSNorm(c["H"], eps=c["eps"]).to(DEV).to(dt)
+    norm.weight.data = norm_w.to(DEV)
+    hd = h.to(DEV)
+
+    xn = norm(hd)
+    ref_xn = cases.from_bits(g[f"normed_{i}"], dt)
+    assert xn.dtype == dt and xn.shape == hd.shape
+    ulp = (2.0 ** -7 if dt == torch.bfloat16 else 2.0 ** -22)       # bound of one unit in the last place, relative
+    diff = (cpu(xn).double() - ref_xn.double()).abs()
+    assert bool((diff <= ulp * ref_xn.double().abs()).all())
+    same_rows = (diff == 0).all(dim=1)
+    assert same_rows.float().mean() >= 0.9
+    if dt == torch.bfloat16:
+        assert (diff != 0).float().mean() <= 1e-3
+    # 3-D input keeps its shape
+    assert torch.equal(norm(hd.reshape(1, *hd.shape)).reshape(hd.shape), xn)
+
+    out = blk.half_layer(hd, norm)
+    assert out.dtype == dt and out.shape == hd.shape
+    # the fused add is the add of two model-dtype tensors
+    assert torch.equal(out, hd + blk(xn))
+    rt, at = (1e-4, 1e-5) if dt == torch.float32 else (RTOL, ATOL)
+    ref_out = cases.from_bits(g[f"out_{i}"], dt)
+    ids, _, _ = moe_router(xn, blk.gate.weight, c["K"], return_int32_ids=True)
+    assert torch.equal(cpu(ids)[same_rows], torch.from_numpy(g[f"ids_{i}"]).to(torch.int64)[same_rows])
+    torch.testing.assert_close(cpu(out)[same_rows].float(), ref_out[same_rows].float(), rtol=rt, atol=at)
+    blk_ref, ids_ref, _, _ = O.block_forward(cpu(xn), lay.router, lay.gate, lay.up, lay.down, c["K"], True)
+    assert torch.equal(cpu(ids), ids_ref)
+    torch.testing.assert_close(cpu(out).float(), (h + blk_ref).float(), rtol=rt, atol=at)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("H", [2048, 4096, 8200, 100])
+def test_rms_norm_row_lengths(dtype, H):
+    """Every code path of the norm kernel (rows in registers at 2/4/8/16 vectors a lane, long and ragged rows)."""
+    g = torch.Generator().manual_seed(H)
+    x = (torch.randn(37, H, generator=g) * 3).to(dtype)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(dtype)
+    got = cpu(rms_norm(x.to(DEV), w.to(DEV), 1e-6))
+    ref = O.rms_norm(x, w, 1e-6)
+    ulp = {torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10, torch.float32: 2.0 ** -22}[dtype]
+    diff = (got.double() - ref.double()).abs()
+    assert bool((diff <= ulp * ref.double().abs() + (6e-8 if dtype == torch.float16 else 0.0)).all())
+    if dtype != torch.float32:
+        assert (diff != 0).float().mean() <= 1e-3
+    assert rms_norm(x[:0].to(DEV), w.to(DEV)).shape == (0, H)

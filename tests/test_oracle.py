@@ -139,3 +139,15 @@ def test_config4_skewed_routing():
     _eq(off, torch.from_numpy(g["offsets"]))
     counts = off[1:] - off[:-1]
     assert int((counts == 0).sum()) >= 1          # the workload leaves some experts empty
+
+
+@pytest.mark.parametrize("i", range(len(cases.GLUE_CASES)))
+def test_decoder_layer_glue(i):
+    """RMSNorm in, residual add out: bit-exact against the reference's own layer arithmetic."""
+    c = cases.GLUE_CASES[i]
+    g = cases.golden("glue_cases")
+    lay, h, norm_w = cases.glue_case_inputs(c)
+    out, xn, ids = O.moe_half_layer(h, norm_w, c["eps"], lay.router, lay.gate, lay.up, lay.down, c["K"])
+    assert torch.equal(xn, cases.from_bits(g[f"normed_{i}"], c["dtype"]))
+    assert torch.equal(ids, torch.from_numpy(g[f"ids_{i}"]))
+    assert torch.equal(out, cases.from_bits(g[f"out_{i}"], c["dtype"]))
