@@ -43,6 +43,7 @@ typedef enum {
 /* bits of the device status word */
 #define MQ_DEV_WAIT_EXPIRED 1u   /* a bounded mbarrier wait gave up; the output is invalid */
 #define MQ_DEV_EP_OVERFLOW 2u    /* an expert-parallel receive buffer was too small; rows were dropped */
+#define MQ_DEV_BAD_LAUNCH 4u     /* a kernel found less shared memory than its layout needs; it did nothing */
 
 int mq_version(void);
 const char* mq_status_string(int status);

@@ -1,10 +1,20 @@
 // Entry points that choose between kernels, and the library's bookkeeping calls.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace mq {
 
 static thread_local cudaError_t g_last_error = cudaSuccess;
 void set_last_cuda_error(cudaError_t e) { g_last_error = e; }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("MQMOE_PDL");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return on;
+}
 
 int grouped_gemm_generic_dispatch(const void* a, const void* w, const int32_t* offsets, int64_t S, int64_t E,
                                   int64_t period, int64_t N, int64_t Kd, int dtype, bool swiglu, void* out,

@@ -57,4 +57,31 @@ template <typename T> __device__ __forceinline__ float swiglu_rounded(float g, f
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
 
+// Programmatic dependent launch.  A kernel launched with launch_after_predecessor() may start while the kernel
+// before it in the stream is still running; it must call pdl_wait() before it touches anything that kernel (or
+// any earlier one) wrote or reads, which blocks until the predecessor has completed and its writes are visible.
+// pdl_release() lets the NEXT kernel of the stream be scheduled from here on (it still waits in its own
+// pdl_wait()).  A kernel that calls neither behaves as in an ordinary launch, so the two kinds mix freely.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// MQMOE_PDL=0 in the environment turns the launch attribute off (every launch then serialises as usual).
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after_predecessor(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace mq

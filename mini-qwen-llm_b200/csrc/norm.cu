@@ -27,6 +27,8 @@ rms_norm_rows(const T* __restrict__ x, const T* __restrict__ weight, float eps, 
   constexpr int V = 16 / sizeof(T);
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_wait();                     // x comes from the kernel before this one
+  pdl_release();
   if (row >= rows) return;
   const int nvec = (int)(H / V);                       // vectors in a row; H is a multiple of V
   const uint4* src = reinterpret_cast<const uint4*>(x + row * H);
@@ -100,10 +102,10 @@ int launch_rms_norm(const void* x, const void* weight, float eps, int64_t rows, 
   const int64_t nvec = H / V;
   if (vectors && nvec <= 32 * 16) {
     const unsigned blocks = (unsigned)((rows + 7) / 8);
-    if (nvec <= 32 * 2) rms_norm_rows<T, 2><<<blocks, 256, 0, st>>>(xs, ws, eps, rows, H, os);
-    else if (nvec <= 32 * 4) rms_norm_rows<T, 4><<<blocks, 256, 0, st>>>(xs, ws, eps, rows, H, os);
-    else if (nvec <= 32 * 8) rms_norm_rows<T, 8><<<blocks, 256, 0, st>>>(xs, ws, eps, rows, H, os);
-    else rms_norm_rows<T, 16><<<blocks, 256, 0, st>>>(xs, ws, eps, rows, H, os);
+    if (nvec <= 32 * 2) launch_after_predecessor(rms_norm_rows<T, 2>, dim3(blocks), dim3(256), 0, st, xs, ws, eps, rows, H, os);
+    else if (nvec <= 32 * 4) launch_after_predecessor(rms_norm_rows<T, 4>, dim3(blocks), dim3(256), 0, st, xs, ws, eps, rows, H, os);
+    else if (nvec <= 32 * 8) launch_after_predecessor(rms_norm_rows<T, 8>, dim3(blocks), dim3(256), 0, st, xs, ws, eps, rows, H, os);
+    else launch_after_predecessor(rms_norm_rows<T, 16>, dim3(blocks), dim3(256), 0, st, xs, ws, eps, rows, H, os);
   } else {
     rms_norm_long_rows<T><<<(unsigned)rows, 256, 0, st>>>(xs, ws, eps, H, os);
   }

@@ -157,6 +157,8 @@ unpermute_combine(const T* __restrict__ rows, const float* __restrict__ weights,
   __shared__ int s_row[32];
   __shared__ float s_w[32];
   const int64_t t = blockIdx.x;
+  pdl_wait();                     // the rows come from the kernel before this one
+  pdl_release();
   if (threadIdx.x < K) {
     s_row[threadIdx.x] = inv[t * K + threadIdx.x];
     s_w[threadIdx.x] = weights[t * K + threadIdx.x];
@@ -202,8 +204,8 @@ int launch_combine(const void* rows, const float* weights, const int32_t* inv, c
                    int K, int64_t H, void* out, cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
   dim3 grid((unsigned)T_, (unsigned)((H + 128 * V - 1) / (128 * V)));
-  unpermute_combine<T><<<grid, 128, 0, st>>>(reinterpret_cast<const T*>(rows), weights, inv,
-                                            reinterpret_cast<const T*>(residual), K, H, reinterpret_cast<T*>(out));
+  launch_after_predecessor(unpermute_combine<T>, grid, dim3(128), 0, st, reinterpret_cast<const T*>(rows), weights, inv,
+                           reinterpret_cast<const T*>(residual), K, H, reinterpret_cast<T*>(out));
   return check_launch();
 }
 

@@ -2,6 +2,8 @@
 // block-level pieces of the expert-sorted permute plan (a stable counting sort of the slots by expert id).
 #pragma once
 
+#include <climits>
+
 #include "common.cuh"
 
 namespace mq {
@@ -64,33 +66,110 @@ __device__ __forceinline__ void softmax_topk_row(const float* __restrict__ p, in
 #pragma unroll
   for (int j = 0; j < EPL; ++j) s[j] = (lane + 32 * j < E) ? s[j] / sum : -1.0f;  // scores >= 0; -1 = absent
 
-  uint32_t taken = 0;
+  // Selection on the scores' bit patterns: a non-negative float orders like its bits read as a signed integer,
+  // so one warp-wide integer maximum finds the best score and one integer minimum over the lanes that hold it
+  // finds the lowest expert id among equals (two reductions per round instead of a shuffle tree on pairs).
+  int key[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) key[j] = (lane + 32 * j < E) ? __float_as_int(s[j]) : INT_MIN;
   float my_w = 0.0f;
   int my_id = 0;
   float wsum = 0.0f;
   for (int k = 0; k < K; ++k) {
-    float best = -2.0f;
-    int best_e = 0x7fffffff;
+    int best = INT_MIN, best_j = 0;
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
       // ascending j = ascending id within the lane, strict > keeps the lower id on ties
-      if (!((taken >> j) & 1u) && s[j] > best) { best = s[j]; best_e = lane + 32 * j; }
+      if (key[j] > best) { best = key[j]; best_j = j; }
     }
+    const int top = __reduce_max_sync(0xffffffffu, best);
+    const int id = __reduce_min_sync(0xffffffffu, best == top ? lane + 32 * best_j : INT_MAX);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-    }
-    if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
-    if (lane == k) { my_w = best; my_id = best_e; }
-    wsum += best;
+    for (int j = 0; j < EPL; ++j)
+      if (lane + 32 * j == id) key[j] = INT_MIN;
+    const float score = __int_as_float(top);
+    if (lane == k) { my_w = score; my_id = id; }
+    wsum += score;
   }
   if (lane < K) {
     float wv = renorm ? my_w / wsum : my_w;
     weights_row[lane] = wv;
     if (ids64_row != nullptr) ids64_row[lane] = my_id;
     if (ids32_row != nullptr) ids32_row[lane] = my_id;
+  }
+}
+
+// The same selection with EIGHT lanes per token, four tokens per warp at a time (for many tokens on few warps).
+// Sub-lane sl of a token's group holds experts sl, sl + 8, ...; the reductions are three-level butterflies inside
+// the group.  The scores' sum runs in another order than in softmax_topk_row, so weights may differ from it in the
+// last place.  All 32 lanes must call it together; a group whose `live` is false computes on its row but stores
+// nothing.  K <= 32, E <= 8 * EPS.
+template <int EPS>
+__device__ __forceinline__ void softmax_topk_sub8(const float* __restrict__ row, const float* __restrict__ bias, int E,
+                                                  int K, int renorm, int sl, bool live,
+                                                  int64_t* __restrict__ ids64_row, int32_t* __restrict__ ids32_row,
+                                                  float* __restrict__ weights_row) {
+  float s[EPS];
+  float m = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < EPS; ++j) {
+    const int e = sl + 8 * j;
+    float v = -INFINITY;
+    if (e < E) {
+      v = row[e];
+      if (bias != nullptr) v += bias[e];
+    }
+    s[j] = v;
+    m = fmaxf(m, v);
+  }
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < EPS; ++j) {
+    const float pe = (sl + 8 * j < E) ? expf(s[j] - m) : 0.0f;
+    s[j] = pe;
+    sum += pe;
+  }
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  int key[EPS];
+#pragma unroll
+  for (int j = 0; j < EPS; ++j) key[j] = (sl + 8 * j < E) ? __float_as_int(s[j] / sum) : INT_MIN;
+  float my_w[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  int my_id[4] = {0, 0, 0, 0};
+  float wsum = 0.0f;
+  for (int k = 0; k < K; ++k) {
+    int best = INT_MIN, id = INT_MAX;
+#pragma unroll
+    for (int j = 0; j < EPS; ++j) {
+      if (key[j] > best) { best = key[j]; id = sl + 8 * j; }
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      const int ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, id, o);
+      if (ob > best || (ob == best && oi < id)) { best = ob; id = oi; }
+    }
+#pragma unroll
+    for (int j = 0; j < EPS; ++j)
+      if (sl + 8 * j == id) key[j] = INT_MIN;
+    const float score = __int_as_float(best);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (k == sl + 8 * q) { my_w[q] = score; my_id[q] = id; }
+    wsum += score;
+  }
+  if (live) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int k = sl + 8 * q;
+      if (k < K) {
+        weights_row[k] = renorm ? my_w[q] / wsum : my_w[q];
+        if (ids64_row != nullptr) ids64_row[k] = my_id[q];
+        if (ids32_row != nullptr) ids32_row[k] = my_id[q];
+      }
+    }
   }
 }
 

@@ -358,12 +358,12 @@ router_softmax_topk(const float* __restrict__ logits, int slices, const float* _
 // Small batches (decode): logits, softmax + top-k, the permute plan and the preparation of the activations
 // for the W4A16 kernels in ONE launch.  At these sizes each of the four kernels runs for a few microseconds
 // and the layer call is bound by the chain of launches, not by any of them.
-//   phase A, every CTA: CTA e forms the logits of expert e for all tokens with the arithmetic of
-//     router_logits_skinny (fp32 FMA chains over lanes' 8-element pieces, shuffle tree), and CTA t < T
-//     also writes token t's row in the k order the W4A16 kernels want, with its group sums;
+//   phase A, every CTA: CTA e forms the logits of expert e for all tokens (fp32 FMA chains over 8-element
+//     pieces, one piece per thread and pass, shuffle tree, then the warps' sums in warp order), and CTA
+//     t < T also writes token t's row in the k order the W4A16 kernels want, with its group sums;
 //   phase B, the CTA that finishes last (a counter in the workspace tells it; nobody waits): softmax and
 //     top-k of every token (one warp per token, softmax_topk_row), then the stable counting sort of the
-//     T*K slots (the code of permute_plan_small).  It leaves the counter at zero for the next call.
+//     T*K slots by expert.  It leaves the counter at zero for the next call.
 constexpr int RSM_THREADS = 512;
 constexpr int RSM_MAX_T = 64, RSM_MAX_E = 256, RSM_MAX_S = 2048;
 
@@ -377,22 +377,28 @@ route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__
                    int64_t* __restrict__ off64, __nv_bfloat16* __restrict__ xp, float* __restrict__ xs) {
   extern __shared__ __align__(16) uint8_t rsm_smem[];
   __shared__ int s_last;
-  __shared__ int s_warp_tot[RSM_THREADS / 32];
+  __shared__ float s_part[8][RSM_MAX_T];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int e = blockIdx.x;
+  pdl_wait();                       // x may come from the kernel before this one
+  pdl_release();
 
-  // ---- phase A: logits of expert e
+  // ---- phase A: logits of expert e.  The K dimension is spread over 256 threads (one 8-element piece each per
+  // pass, so the loads of a thread are independent of one another: one round trip to L2), the tokens over the two
+  // halves of the CTA in chunks of 8.  A warp reduces its partial sums with shuffles; the eight warps of a half
+  // meet in shared memory and are added in warp order.
   {
     const size_t w_row = (size_t)e * H;
     const bool fast = vec_ok && xdt != MQ_F32 && wdt != MQ_F32;     // 16-bit operands, 16-byte pieces
-    for (int tb = warp * 8; tb < T; tb += (RSM_THREADS / 32) * 8) {
+    const int kt = tid & 255, half = tid >> 8, kwarp = kt >> 5;
+    for (int tb = half * 8; tb < T; tb += 16) {
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
       if (fast) {
         const uint16_t* wp = reinterpret_cast<const uint16_t*>(w) + w_row;
         const uint16_t* xq = reinterpret_cast<const uint16_t*>(x);
-        for (int k = lane * 8; k < H; k += 32 * 8) {
+        for (int k = kt * 8; k < H; k += 256 * 8) {
           const uint4 wr = __ldg(reinterpret_cast<const uint4*>(wp + k));
           uint4 xr[8];
 #pragma unroll
@@ -409,7 +415,7 @@ route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__
           }
         }
       } else {
-        for (int64_t k = (int64_t)lane * 8; k < H; k += 32 * 8) {
+        for (int64_t k = (int64_t)kt * 8; k < H; k += 256 * 8) {
           float wv[8];
           load8_safe(w, wdt, w_row, k, H, vec_ok, wv);
 #pragma unroll
@@ -428,8 +434,15 @@ route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__
         float v = acc[i];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && tb + i < T) logits[(size_t)(tb + i) * E + e] = v;
+        if (lane == 0 && tb + i < T) s_part[kwarp][tb + i] = v;
       }
+    }
+    __syncthreads();
+    if (tid < T) {
+      float v = s_part[0][tid];
+#pragma unroll
+      for (int wi = 1; wi < 8; ++wi) v += s_part[wi][tid];
+      logits[(size_t)tid * E + e] = v;
     }
   }
   // ---- phase A: token row e in the k order 0,4,1,5,2,6,3,7 inside every 8, and its sums over every 128 k
@@ -468,37 +481,80 @@ route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__
   __threadfence();
 
   // ---- phase B: the logits of all experts come from L2 into shared memory, then one warp per token
-  float* s_logits = reinterpret_cast<float*>(rsm_smem);                 // [T, E]
-  int* s_ids = reinterpret_cast<int*>(rsm_smem + (size_t)T * E * 4);     // [T * K]
-  int* s_run = s_ids + T * K;                                           // [E]
+  unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(rsm_smem);   // [E] tokens that chose expert e
+  float* s_logits = reinterpret_cast<float*>(s_mask + E);                        // [T, E]
+  int* s_ids = reinterpret_cast<int*>(s_logits + (size_t)T * E);                  // [T * K]
+  int* s_run = s_ids + T * K;                                                    // [E] first sorted slot of expert e
   for (int i = tid; i < T * E; i += RSM_THREADS) s_logits[i] = __ldcg(logits + i);
+  for (int ee = tid; ee < E; ee += RSM_THREADS) s_mask[ee] = 0ull;
   __syncthreads();
-  for (int t = warp; t < T; t += RSM_THREADS / 32)
-    softmax_topk_row<EPL>(s_logits + (size_t)t * E, 1, 0, bias, E, K, renorm, lane,
-                          ids64 ? ids64 + (size_t)t * K : nullptr, s_ids + t * K, weights + (size_t)t * K);
+  if (T <= RSM_THREADS / 32) {
+    for (int t = warp; t < T; t += RSM_THREADS / 32)
+      softmax_topk_row<EPL>(s_logits + (size_t)t * E, 1, 0, bias, E, K, renorm, lane,
+                            ids64 ? ids64 + (size_t)t * K : nullptr, s_ids + t * K, weights + (size_t)t * K);
+  } else {
+    // more tokens than warps: eight lanes per token, so that the 64 tokens of the largest batch are one pass
+    for (int t0 = warp * 4; t0 < T; t0 += RSM_THREADS / 8) {
+      const int t = t0 + (lane >> 3);
+      const bool live = t < T;
+      const int tr = live ? t : T - 1;
+      softmax_topk_sub8<EPL * 4>(s_logits + (size_t)tr * E, bias, E, K, renorm, lane & 7, live,
+                                 ids64 ? ids64 + (size_t)tr * K : nullptr, s_ids + tr * K, weights + (size_t)tr * K);
+    }
+  }
   __syncthreads();
+  // The plan (a stable counting sort of the T*K slots by expert).  A token's K experts are distinct and the
+  // slots are token-major, so the rank of slot (t, k) inside its expert is the number of earlier TOKENS that
+  // chose the expert: with T <= 64 one 64-bit mask per expert holds everything, and no step is serial.
   const int S = T * K;
-  for (int i = tid; i < S; i += RSM_THREADS) ids32[i] = s_ids[i];
-  // the plan: histogram, exclusive scan, stable placement
-  for (int ee = tid; ee < E; ee += RSM_THREADS) s_run[ee] = 0;
+  for (int i = tid; i < S; i += RSM_THREADS) {
+    const int ee = s_ids[i];
+    ids32[i] = ee;
+    atomicOr(&s_mask[ee], 1ull << (i / K));
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // exclusive scan of the E counts: each lane takes E/32 (at most 8) consecutive experts
+    const int per = (E + 31) / 32;
+    int cnt[RSM_MAX_E / 32];
+    int sum = 0;
+#pragma unroll
+    for (int j = 0; j < RSM_MAX_E / 32; ++j) {
+      const int ee = lane * per + j;
+      cnt[j] = (j < per && ee < E) ? __popcll(s_mask[ee]) : 0;
+      sum += cnt[j];
+    }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int j = 0; j < RSM_MAX_E / 32; ++j) {
+      const int ee = lane * per + j;
+      if (j < per && ee < E) {
+        s_run[ee] = run;
+        if (off64) off64[ee] = run;
+        if (off32) off32[ee] = run;
+      }
+      run += cnt[j];
+    }
+    if (lane == 31) {
+      if (off64) off64[E] = incl;
+      if (off32) off32[E] = incl;
+      *counter = 0;                                 // ready for the next call
+    }
+  }
   __syncthreads();
   for (int i = tid; i < S; i += RSM_THREADS) {
     const int ee = s_ids[i];
-    if ((unsigned)ee < (unsigned)E) atomicAdd(&s_run[ee], 1);
+    const int t = i / K;
+    const int pos = s_run[ee] + __popcll(s_mask[ee] & ((1ull << t) - 1ull));
+    perm[pos] = i;
+    inv[i] = pos;
   }
-  __syncthreads();
-  const int total = block_exclusive_scan<RSM_THREADS>(s_run, E, s_warp_tot);
-  for (int ee = tid; ee < E; ee += RSM_THREADS) {
-    if (off64) off64[ee] = s_run[ee];
-    if (off32) off32[ee] = s_run[ee];
-  }
-  if (tid == 0) {
-    if (off64) off64[E] = total;
-    if (off32) off32[E] = total;
-    *counter = 0;                                   // ready for the next call
-  }
-  __syncthreads();
-  place_segment<false, RSM_THREADS>(s_ids, 0, S, E, s_run, perm, inv);
 }
 
 template <int EPL>
@@ -679,6 +735,7 @@ extern "C" int mq_route_small(const void* x, int x_dtype, const void* w, int w_d
   if ((xp != nullptr) != (xs != nullptr)) return MQ_ERR_INVALID_ARGUMENT;
   // the prepared rows are a bf16 format with 128-k groups, 32 of them at most
   if (xp != nullptr && (x_dtype != MQ_BF16 || H % 128 != 0 || H / 128 > 32)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (xp != nullptr && T > E) return MQ_ERR_UNSUPPORTED_SHAPE;     // CTA t prepares token t; there are E CTAs
   if (T == 0) return MQ_OK;
   if (!x || !w || !workspace || !weights || !ids32 || !perm || !inv || (!offsets64 && !offsets32))
     return MQ_ERR_INVALID_ARGUMENT;
@@ -687,12 +744,12 @@ extern "C" int mq_route_small(const void* x, int x_dtype, const void* w, int w_d
   const int vec_ok = (H % 8 == 0) && aligned16(x) && aligned16(w);
   float* logits = reinterpret_cast<float*>(workspace);
   int* counter = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + (size_t)T * E * sizeof(float));
-  const size_t smem = (size_t)T * E * 4 + (size_t)T * K * 4 + (size_t)E * 4;
+  const size_t smem = (size_t)E * 8 + (size_t)T * E * 4 + (size_t)T * K * 4 + (size_t)E * 4;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define MQ_RSM_LAUNCH(EPL)                                                                                       \
   do {                                                                                                           \
     cudaFuncSetAttribute(route_small_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-    route_small_kernel<EPL><<<(unsigned)E, RSM_THREADS, smem, st>>>(                                              \
+    launch_after_predecessor(route_small_kernel<EPL>, dim3((unsigned)E), dim3(RSM_THREADS), smem, st,             \
         x, x_dtype, w, w_dtype, bias, (int)T, (int)H, (int)E, (int)K, renormalize, vec_ok, logits, counter, ids32, \
         ids64, weights, perm, inv, offsets32, offsets64, reinterpret_cast<__nv_bfloat16*>(xp), xs);               \
   } while (0)

@@ -177,6 +177,8 @@ w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
   constexpr int SLOT = W4_NS + 1;                    // 16-byte pieces per lane and k-step: 2 weights + x
   __shared__ uint4 ring[W4_WARPS][W4_DEPTH][SLOT][32];
 
+  pdl_wait();                     // offsets and x come from the kernels before this one
+  pdl_release();
   int e = (int)blockIdx.y;
   if (compact) {
     // the first word of the (still unused) ring carries the expert index from warp 0 to the others
@@ -365,9 +367,9 @@ void launch_w4_variant(const void* x, W4Proj p0, W4Proj p1, const int32_t* offse
   // with fewer slots than experts most experts are empty: index the grid by non-empty experts instead
   const int compact = S < E;
   dim3 grid((unsigned)((N + cols_per_cta - 1) / cols_per_cta), (unsigned)(compact ? S : E));
-  w4a16_grouped_kernel<SWIGLU, KSPLIT><<<grid, W4_WARPS * 32, 0, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), p0, p1, offsets, (int)E, (int)period, (int)N, (int)Kd, (int)group,
-      compact, reinterpret_cast<__nv_bfloat16*>(out));
+  launch_after_predecessor(w4a16_grouped_kernel<SWIGLU, KSPLIT>, grid, dim3(W4_WARPS * 32), 0, st,
+                           reinterpret_cast<const __nv_bfloat16*>(x), p0, p1, offsets, (int)E, (int)period, (int)N,
+                           (int)Kd, (int)group, compact, reinterpret_cast<__nv_bfloat16*>(out));
 }
 
 }  // namespace

@@ -42,6 +42,9 @@
 #include <cuda.h>
 
 #include <mutex>
+#ifdef WS_EXPERIMENT
+#include <cstdlib>
+#endif
 
 #include "common.cuh"
 
@@ -55,9 +58,8 @@ constexpr int WS_MAX_STAGES = 3;
 constexpr int WS_RED_BYTES = WS_CONSUMERS * 16 * 32 * 4;            // partial sums of the K split: 32 KB
 constexpr int WS_MAX_GROUPS = 384;                                  // row groups (experts) the item table can index
 constexpr int WS_TABLE_BYTES = (WS_MAX_GROUPS + 1) * 4;
-constexpr int WS_LIST = 64;                                         // window of item descriptors (16 bytes each)
-constexpr int WS_SMEM_BYTES = WS_RING_BYTES + WS_RED_BYTES + 128 /*alignment*/ + 256 /*barriers*/ + WS_LIST * 16 +
-                              WS_TABLE_BYTES;
+constexpr int WS_LIST = 16;                                         // window of item descriptors (48 bytes each)
+constexpr int WS_SMALL_BYTES = 256 /*barriers*/ + WS_LIST * 48 + WS_TABLE_BYTES;
 constexpr uint32_t WS_SPIN_LIMIT = 1u << 24;
 constexpr uint32_t BF16_ONES2 = 0x3F803F80u;
 
@@ -234,6 +236,12 @@ struct WsItem {
   int rows;       // 1..8
   int ci;         // column item: panels [ci*CW, (ci+1)*CW)
 };
+// An item in the CTA's window: the descriptor and the rows of x its eight block rows come from (a row past the
+// expert's last repeats the first: computed, not stored), looked up once per item instead of once per warp.
+struct WsListed {
+  WsItem it;
+  int src[8];
+};
 
 // Items are numbered in (expert, row block, column item) order.  first_item[e] is the number of the first
 // item of expert e (a table in shared memory, built once per CTA), so an item is found by a binary search.
@@ -288,26 +296,48 @@ __device__ void ws_build_item_table(const int32_t* __restrict__ offsets, int E, 
 // XSHUF: the activations already have the k order 0,4,1,5,2,6,3,7 inside every 8 (mq_w4a16_tc_prep, or the
 //        shuffled output of the SwiGLU variant); otherwise the order is made with four byte permutes per step.
 // XSUM:  the group sums come from P.xs; otherwise from one more MMA pair per step against a tile of ones.
+#ifdef WS_TRACE
+__device__ unsigned long long ws_trace_buf[160 * 8];
+#define WS_TR_DECL long long tr_acc[7] = {0, 0, 0, 0, 0, 0, 0}; long long tr_t = clock64(); const long long tr_start = tr_t
+#define WS_TR(i) do { const long long tr_n = clock64(); tr_acc[i] += tr_n - tr_t; tr_t = tr_n; } while (0)
+#define WS_TR_FLUSH do { if (lane == 0) { tr_acc[6] = clock64() - tr_start; for (int i = 0; i < 7; ++i) atomicAdd(&ws_trace_buf[blockIdx.x * 8 + i], (unsigned long long)tr_acc[i]); } } while (0)
+#else
+#define WS_TR_DECL
+#define WS_TR(i)
+#define WS_TR_FLUSH
+#endif
+
 template <bool SWIGLU, bool XSHUF, bool XSUM>
 __global__ void __launch_bounds__(WS_THREADS, 1)
 w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                     const WsParams P) {
   constexpr int NS = SWIGLU ? 2 : 1;                   // weight streams per warp
-  extern __shared__ uint8_t ws_smem_raw[];
+  extern __shared__ __align__(16) uint8_t ws_smem_raw[];
+  // Layout: barriers, item list and item table first; they fill most of the gap up to the next 1024-byte
+  // boundary, where the ring starts (the copies land with the 128-byte swizzle, whose pattern repeats every
+  // 1024 bytes); the partial sums follow the ring.
   const uint32_t raw = ws_smem_u32(ws_smem_raw);
-  const uint32_t ring = (raw + 127u) & ~127u;
+  uint8_t* bar_mem = ws_smem_raw;
+  const uint32_t bars = raw;
+  const uint32_t ring = (raw + WS_SMALL_BYTES + 1023u) & ~1023u;
   uint8_t* ring_ptr = ws_smem_raw + (ring - raw);
   float* red = reinterpret_cast<float*>(ring_ptr + WS_RING_BYTES);
-  uint8_t* bar_mem = ring_ptr + WS_RING_BYTES + WS_RED_BYTES;
-  const uint32_t bars = ring + WS_RING_BYTES + WS_RED_BYTES;
   // bar_mem: full[3] | abort flag | stage_done[3] ... +128: ready[8] | taken[8] ... +256: item list ... then the table
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto ready_bar = [&](int c) { return bars + 128u + 8u * c; };     // the KW partial sums of panel c are written
   auto taken_bar = [&](int c) { return bars + 192u + 8u * c; };     // ... and have been read again
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * WS_MAX_STAGES);
   int* stage_done = reinterpret_cast<int*>(bar_mem + 8 * WS_MAX_STAGES + 8);   // warps finished with a stage
-  WsItem* list = reinterpret_cast<WsItem*>(bar_mem + 256);          // this CTA's items, a window of WS_LIST of them
-  int* first_item = reinterpret_cast<int*>(bar_mem + 256 + WS_LIST * sizeof(WsItem));
+  WsListed* list = reinterpret_cast<WsListed*>(bar_mem + 256);      // this CTA's items, a window of WS_LIST of them
+  int* first_item = reinterpret_cast<int*>(bar_mem + 256 + WS_LIST * sizeof(WsListed));
+  {
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    if (ring - raw + WS_RING_BYTES + WS_RED_BYTES > dyn_bytes) {     // the launch did not leave room for the alignment
+      if (threadIdx.x == 0 && P.d_status != nullptr) atomicOr(P.d_status, MQ_DEV_BAD_LAUNCH);
+      return;
+    }
+  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KW = P.KW, CW = P.CW, gpw = P.gpw, RS = P.RS, N = P.N, Kd = P.Kd, G = P.G;
@@ -323,21 +353,28 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  pdl_wait();                   // everything above is this kernel's own; from here on it reads the predecessor's outputs
+  pdl_release();
   ws_build_item_table(P.offsets, P.E, P.ipe, first_item);      // ends with a __syncthreads
   const WsItems items{P.offsets, first_item, P.E, P.ipe};
   // items of this CTA: numbers blockIdx.x + q * gridDim.x, q = 0 .. n_mine-1
   const int total_items = first_item[P.E];
   const int n_mine = total_items > (int)blockIdx.x ? (total_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-  // The descriptors of the CTA's items q in [32*floor(q/32), +64) sit in list[q % 64]: one 16-byte read per item
-  // instead of a search plus two dependent global loads by every warp.  A half is refilled when the walk
+  // The descriptors of the CTA's items q in [8*floor(q/8), +16) sit in list[q % 16]: one shared-memory read per
+  // item instead of a search plus dependent global loads by every warp.  A half is refilled when the walk
   // enters the other one.
-  auto fill_list = [&](int q0) {                                 // descriptors q0 .. q0+31, one thread each
-    if (threadIdx.x < WS_LIST / 2) {
-      const int q = q0 + threadIdx.x;
+  auto fill_list = [&](int q0) {                                 // descriptors q0 .. q0+7, eight threads each
+    if (threadIdx.x < (WS_LIST / 2) * 8) {
+      const int q = q0 + (threadIdx.x >> 3), r = threadIdx.x & 7;
       WsItem d;
       d.expert = 0; d.row0 = 0; d.rows = 0; d.ci = 0;
       if (q < n_mine) items.locate(blockIdx.x + q * gridDim.x, d);
-      list[q % WS_LIST] = d;
+      const int row = d.row0 + (r < d.rows ? r : 0);
+      int src = row;
+      if (P.perm != nullptr && d.rows > 0) src = P.perm[row] / P.top_k;
+      WsListed& e = list[q % WS_LIST];
+      if (r == 0) e.it = d;
+      e.src[r] = src;
     }
   };
   fill_list(0);
@@ -351,7 +388,7 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   auto load_stage = [&](int n) {
     const int q = n / P.spi, sj = n - q * P.spi;
     if (q >= n_mine) return;
-    const WsItem fi = list[q % WS_LIST];
+    const WsItem fi = list[q % WS_LIST].it;
     const int slot = n % P.nst;
     const uint32_t dst = ring + (uint32_t)slot * P.stage_bytes;
     const int we = fi.expert % P.period;
@@ -369,12 +406,8 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   uint32_t phase = 0;
   bool ok = true;
   const int g_first = kw * gpw;                               // this warp's first group of every item
-  // row of x this lane multiplies in an item (rows past the expert's last repeat its first: computed, not stored)
-  auto x_row_of = [&](const WsItem& w) {
-    const int rr = g < w.rows ? g : 0;
-    const int src = P.perm != nullptr ? P.perm[w.row0 + rr] / P.top_k : w.row0 + rr;
-    return P.x + (size_t)src * Kd + 8 * kq;
-  };
+  // row of x this lane multiplies in an item
+  auto x_row_of = [&](const WsListed& w) { return P.x + (size_t)w.src[g] * Kd + 16 * kq; };
 
   // ---- finishing an item: the KW partial sums of every output meet in shared memory
   // (red[cw][stream][element][kw][lane]); each warp of the panel adds up a share of the outputs in a fixed
@@ -393,7 +426,7 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     }
   };
   auto finish = [&](const Pending& f) {
-    if (ok) ok = ws_mbar_wait(ready_bar(cw), (uint32_t)(f.q & 1), abort_flag, P.d_status);
+    if (ok) ok = ws_mbar_wait(ready_bar(cw), (uint32_t)(f.q & 1), abort_flag, P.d_status);   // returns at once if complete
     if (ok) {
       for (int idx = kw; idx < 8; idx += KW) {
         const float* src = red + ((size_t)(cw * NS * 8 + idx) * KW) * 32 + lane;
@@ -421,13 +454,14 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   WsItem it;
   const __nv_bfloat16* xrow = nullptr;
   if (n_mine > 0) {
-    it = list[0];
-    xrow = x_row_of(it);
+    it = list[0].it;
+    xrow = x_row_of(list[0]);
     if (g_first < G) {
       xa[0] = ws_ldg128(xrow + g_first * 128);
-      xa[1] = ws_ldg128(xrow + g_first * 128 + 32);
+      xa[1] = ws_ldg128(xrow + g_first * 128 + 8);
     }
   }
+  WS_TR_DECL;
   for (int q = 0; q < n_mine; ++q) {
     if (q > 0 && (q & (WS_LIST / 2 - 1)) == 0) {                 // entering the other half of the window: refill this one's predecessor
       __syncthreads();
@@ -438,8 +472,9 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     WsItem it_next = it;
     const __nv_bfloat16* xrow_next = xrow;
     if (have_next_item) {
-      it_next = list[(q + 1) % WS_LIST];
-      xrow_next = x_row_of(it_next);
+      const WsListed& ln = list[(q + 1) % WS_LIST];
+      it_next = ln.it;
+      xrow_next = x_row_of(ln);
     }
     const int we = it.expert % P.period;
     const int panel = it.ci * CW + cw;
@@ -451,10 +486,8 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     const float* xsrow = nullptr;
     int xs_delta = 0;
     if (XSUM) {
-      const int r0 = 2 * kq < it.rows ? 2 * kq : 0;
-      const int r1 = 2 * kq + 1 < it.rows ? 2 * kq + 1 : 0;
-      const int s0 = P.perm != nullptr ? P.perm[it.row0 + r0] / P.top_k : it.row0 + r0;
-      const int s1 = P.perm != nullptr ? P.perm[it.row0 + r1] / P.top_k : it.row0 + r1;
+      const WsListed& lc = list[q % WS_LIST];
+      const int s0 = lc.src[2 * kq], s1 = lc.src[2 * kq + 1];
       xsrow = P.xs + (size_t)s0 * 32;
       xs_delta = (s1 - s0) * 32;
     }
@@ -466,10 +499,16 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
       for (int m = 0; m < 2; ++m)
 #pragma unroll
         for (int i = 0; i < 4; ++i) { st[j].master[m][i] = 0.0f; st[j].grp[m][i] = 0.0f; }
+    WS_TR(0);
     for (int sj = 0; sj < P.spi; ++sj) {
       if (ok) ok = ws_mbar_wait(full_bar(stage), phase, abort_flag, P.d_status);
+      WS_TR(1);
       const uint8_t* sbase = ring_ptr + (size_t)stage * P.stage_bytes + (size_t)cw * RS * 128;
+#ifdef WS_ABL_LOADONLY
+      if (false) {
+#else
       if (ok) {
+#endif
         for (int j = 0; j < gpw; ++j) {
           const int gi = (sj * KW + kw) * gpw + j;
           if (gi >= G) break;
@@ -478,7 +517,7 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
 #pragma unroll
           for (int q2 = 0; q2 < NS; ++q2) mc[q2] = ws_meta_fetch(proj[q2], meta_row0 + gi, N, colc);
           xb[0] = ws_ldg128(xrow + gi * 128 + 64);
-          xb[1] = ws_ldg128(xrow + gi * 128 + 96);
+          xb[1] = ws_ldg128(xrow + gi * 128 + 72);
           // the group after this one: next j in this stage, or this warp's first group of the next stage
           int gn = gi + 1;
           if (j + 1 == gpw) gn = ((sj + 1) * KW + kw) * gpw;
@@ -494,13 +533,16 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
             xs[0] = xsrow[gi];
             xs[1] = xsrow[xs_delta + gi];
           }
-          const uint8_t* rows = sbase + (size_t)((kw * gpw + j) * 16 + kq) * 128 + g * 16;
+          // Step s of a group takes word row 8*(s >> 1) + 2*kq + (s & 1) of the group's sixteen (k = 8 x word row):
+          // with the swizzle the eight lanes of a quarter warp then read eight different 16-byte positions.
+          const uint8_t* rows = sbase + (size_t)((kw * gpw + j) * 16 + 2 * kq) * 128;
+          const uint32_t piece[2] = {(uint32_t)((g ^ (2 * kq)) << 4), (uint32_t)((g ^ (2 * kq + 1)) << 4)};
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
             const uint4 xv = s < 2 ? xa[s] : xb[s - 2];
             if (s == 2 && have_next) {                          // xa is free: fetch the next group's first half
               xa[0] = ws_ldg128(xnext + gn * 128);
-              xa[1] = ws_ldg128(xnext + gn * 128 + 32);
+              xa[1] = ws_ldg128(xnext + gn * 128 + 8);
             }
             uint32_t b[4] = {xv.x, xv.y, xv.z, xv.w};
             if (!XSHUF) {
@@ -514,11 +556,12 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
               ws_mma(xs, BF16_ONES2, BF16_ONES2, BF16_ONES2, BF16_ONES2, b[2], b[3]);
             }
             {
-              const uint4 wv = *reinterpret_cast<const uint4*>(rows + s * 512);
+              const uint4 wv = *reinterpret_cast<const uint4*>(rows + (s >> 1) * 1024 + (s & 1) * 128 + piece[s & 1]);
               ws_step(st[0], wv, b);
             }
             if (SWIGLU) {
-              const uint4 wv = *reinterpret_cast<const uint4*>(rows + s * 512 + proj_bytes);
+              const uint4 wv =
+                  *reinterpret_cast<const uint4*>(rows + (s >> 1) * 1024 + (s & 1) * 128 + piece[s & 1] + proj_bytes);
               ws_step(st[NS - 1], wv, b);
             }
           }
@@ -526,10 +569,14 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
           for (int q2 = 0; q2 < NS; ++q2) ws_flush(st[q2], mc[q2], xs[0], xs[1]);
         }
       }
-      if (sj == 0 && have_pend) {                                // the previous item's outputs
+      WS_TR(2);
+      // the previous item's outputs: as soon as the other warps' partial sums are there (a test, not a wait),
+      // at the latest in this item's last stage
+      if (have_pend && (sj + 1 == P.spi || ws_mbar_try_wait(ready_bar(cw), (uint32_t)(pend.q & 1)))) {
         finish(pend);
         have_pend = false;
       }
+      WS_TR(4);
       // Done with the stage.  The last warp to get here refills the slot with the stage nst further on.
       __syncwarp();
       if (lane == 0) {
@@ -542,6 +589,7 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
       }
       ++nstage;
       if (++stage == P.nst) { stage = 0; phase ^= 1u; }
+      WS_TR(3);
     }
     Pending cur_f;
     cur_f.row0 = it.row0; cur_f.rows = it.rows; cur_f.col = col; cur_f.q = q;
@@ -564,8 +612,11 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     }
     it = it_next;
     xrow = xrow_next;
+    WS_TR(5);
   }
   if (have_pend) finish(pend);
+  WS_TR(4);
+  WS_TR_FLUSH;
 }
 
 // ---------------------------------------------------------------------------------------------- host
@@ -587,7 +638,8 @@ WsEncodeTiledFn ws_encode_fn() {
 }
 
 // qweight [period, Kd/8, N] int32 seen as (32 columns, Kd/8 word rows, N/32 panels, period); a box is
-// (32, box_rows, box_panels, 1) and lands as box_panels dense panels of box_rows 128-byte rows.  Word rows
+// (32, box_rows, box_panels, 1) and lands as box_panels dense panels of box_rows 128-byte rows, the 16-byte
+// pieces of a row exchanged by the 128-byte swizzle (piece c of row r sits at position c ^ (r & 7)).  Word rows
 // and panels outside the tensor read as zero.
 bool ws_make_map(CUtensorMap* map, const void* qweight, int64_t period, int64_t Kd, int64_t N, int box_rows,
                  int box_panels) {
@@ -598,9 +650,29 @@ bool ws_make_map(CUtensorMap* map, const void* qweight, int64_t period, int64_t 
   cuuint32_t box[4] = {32, (cuuint32_t)box_rows, (cuuint32_t)box_panels, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, const_cast<void*>(qweight), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+// Dynamic shared memory of a launch: the small structures, the gap up to the ring's 1024-byte boundary and the
+// ring with the partial sums.  The dynamic area starts after the driver's reserved bytes and the kernel's static
+// variables; the kernel re-checks the room it finds.  Sets the kernel's limit; 0 if the device cannot give it.
+int ws_dynamic_smem_bytes(const void* kernel) {
+  cudaFuncAttributes fa;
+  if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) return 0;
+  int dev = 0, reserved = 0, optin = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev);
+  cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  const int start = reserved + (((int)fa.sharedSizeBytes + 15) & ~15);          // where the dynamic area begins
+  const int ring = (start + WS_SMALL_BYTES + 1023) & ~1023;
+  int need = ring - start + WS_RING_BYTES + WS_RED_BYTES;
+  const int room = optin - (int)fa.sharedSizeBytes;
+  if (need > room) return 0;
+  // whatever is left goes in as well: it costs nothing (one CTA per SM) and covers a start the estimate missed
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, room) != cudaSuccess) return 0;
+  return room;
 }
 
 int ws_sm_count() {
@@ -647,6 +719,9 @@ int w4a16_stream(const void* x, const float* xs, bool x_shuffled, const int32_t*
     // 16 panels = no K split at all (no partial sums to add up): worth fewer items per SM
     if (items >= (c == 16 ? 3 : 4) * ws_sm_count()) { CW = c; break; }
   }
+#ifdef WS_EXPERIMENT
+  if (const char* ev = getenv("MQ_WS_CW")) { const int c = atoi(ev); if (c == 1 || c == 2 || c == 4 || (!swiglu && (c == 8 || c == 16))) CW = c; }
+#endif
   const int KW = WS_CONSUMERS / CW;
   // groups per warp and stage: as many as keep a stage within 64 KB (SwiGLU: two projections) / 96 KB
   const int per_group_bytes = nproj * 128 * 16 * KW * CW;          // stage bytes for gpw = 1
@@ -692,9 +767,10 @@ int w4a16_stream(const void* x, const float* xs, bool x_shuffled, const int32_t*
   const bool xsum = xs != nullptr;
 #define MQ_WS_LAUNCH(SW, XSH, XSU)                                                                                 \
   do {                                                                                                             \
-    cudaFuncSetAttribute(w4a16_stream_kernel<SW, XSH, XSU>, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
-                         WS_SMEM_BYTES);                                                                           \
-    w4a16_stream_kernel<SW, XSH, XSU><<<grid, WS_THREADS, WS_SMEM_BYTES, st>>>(map0, map1, P);                      \
+    static const int smem = ws_dynamic_smem_bytes(reinterpret_cast<const void*>(w4a16_stream_kernel<SW, XSH, XSU>)); \
+    if (smem <= 0) return MQ_ERR_LAUNCH_FAILED;                                                                    \
+    launch_after_predecessor(w4a16_stream_kernel<SW, XSH, XSU>, dim3(grid), dim3(WS_THREADS), (size_t)smem, st,    \
+                             map0, map1, P);                                                                       \
   } while (0)
   if (swiglu) {
     if (x_shuffled && xsum) MQ_WS_LAUNCH(true, true, true);
@@ -712,3 +788,15 @@ int w4a16_stream(const void* x, const float* xs, bool x_shuffled, const int32_t*
 }
 
 }  // namespace mq
+
+#ifdef WS_TRACE
+// experiment builds only: per-CTA cycle sums of the stream kernel's phases (reset != 0 clears them)
+extern "C" int mq_debug_ws_trace(void* host_buf, int reset) {
+  if (host_buf) cudaMemcpyFromSymbol(host_buf, mq::ws_trace_buf, sizeof(unsigned long long) * 160 * 8);
+  if (reset) {
+    static unsigned long long zeros[160 * 8] = {0};
+    cudaMemcpyToSymbol(mq::ws_trace_buf, zeros, sizeof(zeros));
+  }
+  return 0;
+}
+#endif

@@ -88,7 +88,7 @@ class Qwen3MoEBlock(nn.Module):
         # top-k and the plan on its own, which pays up to 16 tokens (batch 1: 42.7 against 45.5 us per layer
         # call) and costs from there on (batch 64: 152.7 against 146.8 us)
         self.fuse_small_batches = True
-        self.fuse_max_tokens = 16
+        self.fuse_max_tokens = 64
         self._route_ws = None
         self._peer = None
         self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
@@ -243,7 +243,7 @@ class Qwen3MoEBlock(nn.Module):
         if (self.fuse_small_batches and self.ep_size == 1 and T <= self.fuse_max_tokens
                 and route_small_supported(T, E, K)):
             # decode batches: logits, top-k, plan and the W4A16 activation preparation in one launch
-            prepare = st["w4"] and x2d.dtype == torch.bfloat16 and self._w4_stream(st)
+            prepare = st["w4"] and x2d.dtype == torch.bfloat16 and self._w4_stream(st) and T <= E
             if self._route_ws is None or self._route_ws.device != x2d.device:
                 self._route_ws = route_small_workspace(E, x2d.device)     # zero-filled once, reused by every call
             ids32, weights, perm, inv, off32, xp_tok, xs_tok = run(
