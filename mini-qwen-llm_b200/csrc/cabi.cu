@@ -11,7 +11,7 @@ void set_last_cuda_error(cudaError_t e) { g_last_error = e; }
 bool pdl_enabled() {
   static const bool on = [] {
     const char* v = getenv("MQMOE_PDL");
-    return !(v != nullptr && v[0] == '0');
+    return v != nullptr && v[0] == '1';
   }();
   return on;
 }

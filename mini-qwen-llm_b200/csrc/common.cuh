@@ -65,7 +65,9 @@ __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// MQMOE_PDL=0 in the environment turns the launch attribute off (every launch then serialises as usual).
+// The launch attribute is OFF unless MQMOE_PDL=1 is in the environment (every launch then serialises as usual and
+// the two instructions are no-ops): measured on the decode chain it changes a single-GPU layer call by less than
+// two percent either way and makes the expert-parallel 48-layer pass 12 % slower.
 bool pdl_enabled();
 
 template <typename... KArgs, typename... Args>

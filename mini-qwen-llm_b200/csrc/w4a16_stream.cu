@@ -42,9 +42,6 @@
 #include <cuda.h>
 
 #include <mutex>
-#ifdef WS_EXPERIMENT
-#include <cstdlib>
-#endif
 
 #include "common.cuh"
 
@@ -72,6 +69,16 @@ __device__ __forceinline__ void ws_mbar_expect_tx(uint32_t bar, uint32_t bytes) 
 }
 __device__ __forceinline__ void ws_mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Has the phase of that parity completed?  Never suspends the thread (try_wait may, for a while).
+__device__ __forceinline__ bool ws_mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
 }
 __device__ __forceinline__ bool ws_mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -296,17 +303,6 @@ __device__ void ws_build_item_table(const int32_t* __restrict__ offsets, int E, 
 // XSHUF: the activations already have the k order 0,4,1,5,2,6,3,7 inside every 8 (mq_w4a16_tc_prep, or the
 //        shuffled output of the SwiGLU variant); otherwise the order is made with four byte permutes per step.
 // XSUM:  the group sums come from P.xs; otherwise from one more MMA pair per step against a tile of ones.
-#ifdef WS_TRACE
-__device__ unsigned long long ws_trace_buf[160 * 8];
-#define WS_TR_DECL long long tr_acc[7] = {0, 0, 0, 0, 0, 0, 0}; long long tr_t = clock64(); const long long tr_start = tr_t
-#define WS_TR(i) do { const long long tr_n = clock64(); tr_acc[i] += tr_n - tr_t; tr_t = tr_n; } while (0)
-#define WS_TR_FLUSH do { if (lane == 0) { tr_acc[6] = clock64() - tr_start; for (int i = 0; i < 7; ++i) atomicAdd(&ws_trace_buf[blockIdx.x * 8 + i], (unsigned long long)tr_acc[i]); } } while (0)
-#else
-#define WS_TR_DECL
-#define WS_TR(i)
-#define WS_TR_FLUSH
-#endif
-
 template <bool SWIGLU, bool XSHUF, bool XSUM>
 __global__ void __launch_bounds__(WS_THREADS, 1)
 w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
@@ -461,7 +457,6 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
       xa[1] = ws_ldg128(xrow + g_first * 128 + 8);
     }
   }
-  WS_TR_DECL;
   for (int q = 0; q < n_mine; ++q) {
     if (q > 0 && (q & (WS_LIST / 2 - 1)) == 0) {                 // entering the other half of the window: refill this one's predecessor
       __syncthreads();
@@ -499,16 +494,10 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
       for (int m = 0; m < 2; ++m)
 #pragma unroll
         for (int i = 0; i < 4; ++i) { st[j].master[m][i] = 0.0f; st[j].grp[m][i] = 0.0f; }
-    WS_TR(0);
     for (int sj = 0; sj < P.spi; ++sj) {
       if (ok) ok = ws_mbar_wait(full_bar(stage), phase, abort_flag, P.d_status);
-      WS_TR(1);
       const uint8_t* sbase = ring_ptr + (size_t)stage * P.stage_bytes + (size_t)cw * RS * 128;
-#ifdef WS_ABL_LOADONLY
-      if (false) {
-#else
       if (ok) {
-#endif
         for (int j = 0; j < gpw; ++j) {
           const int gi = (sj * KW + kw) * gpw + j;
           if (gi >= G) break;
@@ -569,14 +558,12 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
           for (int q2 = 0; q2 < NS; ++q2) ws_flush(st[q2], mc[q2], xs[0], xs[1]);
         }
       }
-      WS_TR(2);
       // the previous item's outputs: as soon as the other warps' partial sums are there (a test, not a wait),
       // at the latest in this item's last stage
-      if (have_pend && (sj + 1 == P.spi || ws_mbar_try_wait(ready_bar(cw), (uint32_t)(pend.q & 1)))) {
+      if (have_pend && (sj + 1 == P.spi || ws_mbar_test(ready_bar(cw), (uint32_t)(pend.q & 1)))) {
         finish(pend);
         have_pend = false;
       }
-      WS_TR(4);
       // Done with the stage.  The last warp to get here refills the slot with the stage nst further on.
       __syncwarp();
       if (lane == 0) {
@@ -589,7 +576,6 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
       }
       ++nstage;
       if (++stage == P.nst) { stage = 0; phase ^= 1u; }
-      WS_TR(3);
     }
     Pending cur_f;
     cur_f.row0 = it.row0; cur_f.rows = it.rows; cur_f.col = col; cur_f.q = q;
@@ -612,11 +598,8 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     }
     it = it_next;
     xrow = xrow_next;
-    WS_TR(5);
   }
   if (have_pend) finish(pend);
-  WS_TR(4);
-  WS_TR_FLUSH;
 }
 
 // ---------------------------------------------------------------------------------------------- host
@@ -719,9 +702,6 @@ int w4a16_stream(const void* x, const float* xs, bool x_shuffled, const int32_t*
     // 16 panels = no K split at all (no partial sums to add up): worth fewer items per SM
     if (items >= (c == 16 ? 3 : 4) * ws_sm_count()) { CW = c; break; }
   }
-#ifdef WS_EXPERIMENT
-  if (const char* ev = getenv("MQ_WS_CW")) { const int c = atoi(ev); if (c == 1 || c == 2 || c == 4 || (!swiglu && (c == 8 || c == 16))) CW = c; }
-#endif
   const int KW = WS_CONSUMERS / CW;
   // groups per warp and stage: as many as keep a stage within 64 KB (SwiGLU: two projections) / 96 KB
   const int per_group_bytes = nproj * 128 * 16 * KW * CW;          // stage bytes for gpw = 1
@@ -789,14 +769,3 @@ int w4a16_stream(const void* x, const float* xs, bool x_shuffled, const int32_t*
 
 }  // namespace mq
 
-#ifdef WS_TRACE
-// experiment builds only: per-CTA cycle sums of the stream kernel's phases (reset != 0 clears them)
-extern "C" int mq_debug_ws_trace(void* host_buf, int reset) {
-  if (host_buf) cudaMemcpyFromSymbol(host_buf, mq::ws_trace_buf, sizeof(unsigned long long) * 160 * 8);
-  if (reset) {
-    static unsigned long long zeros[160 * 8] = {0};
-    cudaMemcpyToSymbol(mq::ws_trace_buf, zeros, sizeof(zeros));
-  }
-  return 0;
-}
-#endif

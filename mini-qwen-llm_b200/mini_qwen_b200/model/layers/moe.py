@@ -83,10 +83,9 @@ class Qwen3MoEBlock(nn.Module):
         # "mma" = both projections on the cp.async kernel from materialised rows; "tc" = the tcgen05 kernel
         # with the weights dequantised into tensor memory; "auto" = "tc" by the number of slots per expert
         self.w4_kernel = "stream"
-        # small batches: router, top-k, permute plan (and the W4A16 activation preparation) as ONE launch
-        # instead of three or four (single GPU; same ids and plan, weights equal up to the order of the fp32 logit sums).  The last CTA to finish does the
-        # top-k and the plan on its own, which pays up to 16 tokens (batch 1: 42.7 against 45.5 us per layer
-        # call) and costs from there on (batch 64: 152.7 against 146.8 us)
+        # small batches (up to 64 tokens): router, top-k, permute plan (and, on one GPU, the W4A16 activation
+        # preparation) as ONE launch instead of three or four; same ids and plan, weights equal up to the order of
+        # the fp32 logit sums
         self.fuse_small_batches = True
         self.fuse_max_tokens = 64
         self._route_ws = None
@@ -240,10 +239,10 @@ class Qwen3MoEBlock(nn.Module):
 
         run = self._stage
         xp_tok = xs_tok = None
-        if (self.fuse_small_batches and self.ep_size == 1 and T <= self.fuse_max_tokens
-                and route_small_supported(T, E, K)):
-            # decode batches: logits, top-k, plan and the W4A16 activation preparation in one launch
-            prepare = st["w4"] and x2d.dtype == torch.bfloat16 and self._w4_stream(st) and T <= E
+        if self.fuse_small_batches and 0 < T <= self.fuse_max_tokens and route_small_supported(T, E, K):
+            # decode batches: logits, top-k, plan and (one GPU) the W4A16 activation preparation in one launch
+            prepare = (self.ep_size == 1 and st["w4"] and x2d.dtype == torch.bfloat16 and self._w4_stream(st)
+                       and T <= E)
             if self._route_ws is None or self._route_ws.device != x2d.device:
                 self._route_ws = route_small_workspace(E, x2d.device)     # zero-filled once, reused by every call
             ids32, weights, perm, inv, off32, xp_tok, xs_tok = run(
