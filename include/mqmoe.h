@@ -103,9 +103,10 @@ int mq_router_topk_static(const void* x, int x_dtype, const void* w, int w_dtype
  *     a workspace must not overlap on the GPU;
  *   ids32 int32 [T,K] (required), ids64 int64 [T,K] (optional), weights fp32 [T,K], perm/inv int32 [T*K],
  *     offsets64 / offsets32 [E+1] (one may be NULL);
- *   xp bf16 [T,H] and xs fp32 [T,32], both or neither: every token row in the k order 0,4,1,5,2,6,3,7 inside
- *     every 8 and its sums over every 128 k, the per-token form of what mq_w4a16_tc_prep writes (bf16 x only,
- *     H % 128 == 0, H <= 4096).
+ *   xp [T,H] (16-bit) and xs fp32 [T,32], both or neither: every token row in the k order 0,4,1,5,2,6,3,7
+ *     inside every 8 and its sums over every 128 k, the per-token form of what mq_w4a16_tc_prep writes with
+ *     shuffle = xp_format (1: bf16 as it is; 2: fp16 scaled by the row's power of two, H <= 3968); bf16 x
+ *     only, H % 128 == 0, H <= 4096.
  * Limits: T <= 64, E <= 256, K <= 32, T*K <= 2048 (MQ_ERR_UNSUPPORTED_SHAPE otherwise).
  */
 size_t mq_route_small_workspace_bytes(int64_t T, int64_t E);
@@ -113,7 +114,7 @@ int mq_route_small(const void* x, int x_dtype, const void* w, int w_dtype, const
                    int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
                    void* workspace, size_t workspace_bytes, int64_t* ids64, int32_t* ids32,
                    float* weights, int32_t* perm, int32_t* inv, int64_t* offsets64, int32_t* offsets32,
-                   void* xp, float* xs, void* stream);
+                   void* xp, float* xs, int xp_format, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Permute plan.  Replaces the index work of moe_permute / moe_unpermute
@@ -258,24 +259,28 @@ int mq_w4a16_grouped_swiglu(const void* x,
 
 /* The same two operations with PREPARED activations, the form the block's decode path uses (same results as
  * the two calls above up to the order of the fp32 sums):
- *   xp bf16 [S,Kd]: the expert-sorted rows; x_shuffled != 0: with the k order 0,4,1,5,2,6,3,7 inside every 8
- *     (what mq_w4a16_tc_prep writes with shuffle = 1, and what mq_w4a16_stream_swiglu writes with
- *     shuffle_out != 0), which saves the kernel four byte permutes per 32 k;
+ *   xp [S,Kd] (16-bit): the expert-sorted rows.  x_format 0: bf16, natural k order.  1: bf16 with the k order
+ *     0,4,1,5,2,6,3,7 inside every 8 (what mq_w4a16_tc_prep writes with shuffle = 1, and what
+ *     mq_w4a16_stream_swiglu writes with shuffle_out != 0), which saves the kernel four byte permutes per
+ *     32 k.  2: that order in fp16, every row scaled by a power of two whose inverse sits in xs[row][31]
+ *     (mq_w4a16_tc_prep with shuffle = 2; needs xs, Kd <= 3968): fp16 nibbles unpack with five instead of
+ *     seven integer instructions per weight word, and the scaling is exact, so the results equal format 1's
+ *     except where an element more than 2^28 times smaller than its row's largest loses low bits;
  *   xs fp32 [S,32] or NULL: the rows' sums over every quantisation group (mq_w4a16_tc_prep); given, the
- *     kernel skips the extra MMA pair per 32 k that otherwise forms them; requires x_shuffled;
+ *     kernel skips the extra MMA pair per 32 k that otherwise forms them; requires x_format != 0;
  *   shuffle_out != 0: h is written with its columns in the shuffled order, ready to be the xp of the down
- *     projection (pass x_shuffled = 1 there);
+ *     projection (pass x_format = 1 there);
  *   perm (mq_w4a16_stream_swiglu, optional): xp and xs then hold one row per TOKEN and row p of the expert-sorted
  *     order is row perm[p] / top_k of them, gathered inside the kernel (what mq_route_small prepares).
  * group_size == 128, N % 32 == 0, at most 384 row groups (MQ_ERR_UNSUPPORTED_SHAPE otherwise).  d_status
  * (optional) receives MQ_DEV_WAIT_EXPIRED if a bounded wait on a bulk copy ran out. */
-int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shuffled, const int32_t* perm, int64_t top_k,
+int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_format, const int32_t* perm, int64_t top_k,
                            const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
                            const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
                            const int32_t* offsets, int64_t S, int64_t E, int64_t weight_period, int64_t I,
                            int64_t H, int64_t group_size, int shuffle_out, void* h, int32_t* d_status,
                            void* stream);
-int mq_w4a16_stream_gemm(const void* xp, const float* xs, int x_shuffled, const int32_t* qweight,
+int mq_w4a16_stream_gemm(const void* xp, const float* xs, int x_format, const int32_t* qweight,
                          const void* scales, const int32_t* qzeros, const int32_t* offsets, int64_t S,
                          int64_t E, int64_t weight_period, int64_t N, int64_t Kd, int64_t group_size,
                          void* out, int32_t* d_status, void* stream);
@@ -284,10 +289,13 @@ int mq_w4a16_stream_gemm(const void* xp, const float* xs, int x_shuffled, const 
  * is correct; it is tuned for groups of at most 32 rows).  The packed weights stream in by TMA in
  * the checkpoint layout, are turned into bf16 in registers and written to tensor memory, from where
  * the MMA reads them; the activations must be PREPARED first:
- * mq_w4a16_tc_prep: x bf16 [T,Kd] -> xp bf16 [S,Kd], row r = x[perm[r]/top_k] (perm NULL: x[r],
+ * mq_w4a16_tc_prep: x bf16 [T,Kd] -> xp [S,Kd] (16-bit), row r = x[perm[r]/top_k] (perm NULL: x[r],
  *   S = T) with the k order 0,4,1,5,2,6,3,7 inside every 8 when `shuffle` != 0, and
  *   xs fp32 [S,32]: xs[r][g] = sum of the row over quantisation group g (Kd <= 4096).  xp may be
  *   NULL (sums only: the output of mq_w4a16_tc_swiglu is already in the shuffled order).
+ *   shuffle = 2 (the stream kernels' fp16 format, Kd <= 3968): the shuffled row is multiplied by the power
+ *   of two 2^e that puts its largest magnitude into [2^14, 2^15) and stored as fp16; xs holds the sums of
+ *   the stored values and xs[r][31] = 2^-e.
  * mq_w4a16_tc_swiglu: h_shuffled[r,:] = the fused gate/up + SwiGLU row of mq_w4a16_grouped_swiglu with
  *   its columns in the shuffled k order, ready to be the xp of the down projection.
  * mq_w4a16_tc_gemm: out[r,:] as mq_w4a16_grouped_gemm, natural column order.

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "w4_prep.cuh"
 #include "route_helpers.cuh"
 
 namespace mq {
@@ -374,7 +375,8 @@ route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__
                    float* __restrict__ logits, int* __restrict__ counter,
                    int32_t* __restrict__ ids32, int64_t* __restrict__ ids64, float* __restrict__ weights,
                    int32_t* __restrict__ perm, int32_t* __restrict__ inv, int32_t* __restrict__ off32,
-                   int64_t* __restrict__ off64, __nv_bfloat16* __restrict__ xp, float* __restrict__ xs) {
+                   int64_t* __restrict__ off64, __nv_bfloat16* __restrict__ xp, float* __restrict__ xs,
+                   int prep_mode) {
   extern __shared__ __align__(16) uint8_t rsm_smem[];
   __shared__ int s_last;
   __shared__ float s_part[8][RSM_MAX_T];
@@ -445,30 +447,35 @@ route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__
       logits[(size_t)tid * E + e] = v;
     }
   }
-  // ---- phase A: token row e in the k order 0,4,1,5,2,6,3,7 inside every 8, and its sums over every 128 k
-  // (the arithmetic of the stand-alone preparation kernel: eight adds per 16-byte piece, then a shuffle
-  // tree over the 16 lanes of a group)
+  // ---- phase A: token row e prepared for the W4A16 kernels (w4_prep.cuh: the k order 0,4,1,5,2,6,3,7 inside
+  // every 8, bf16 as it is or fp16 scaled by the row's power of two) and its sums over every 128 k
   if (xp != nullptr && e < T) {
     const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)e * H);
     uint4* o = reinterpret_cast<uint4*>(xp + (size_t)e * H);
+    const bool f16 = prep_mode == 2;
+    float scale = 1.0f;
+    if (f16) {
+      float amax = 0.0f;
+      for (int c = tid; c < H / 8; c += RSM_THREADS) amax = fmaxf(amax, w4_piece_amax(in[c]));
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+      __syncthreads();                           // s_part is free again: the logits were formed above
+      if (lane == 0) s_part[0][warp] = amax;
+      __syncthreads();
+      amax = 0.0f;
+#pragma unroll
+      for (int wi = 0; wi < RSM_THREADS / 32; ++wi) amax = fmaxf(amax, s_part[0][wi]);
+      const int ex = w4_row_exponent(amax);
+      scale = w4_pow2(ex);
+      if (tid == 0) xs[(size_t)e * W4_XS_STRIDE + W4_XS_UNSCALE] = w4_pow2(-ex);
+    }
     for (int c0 = warp * 32; c0 < H / 8; c0 += RSM_THREADS) {
       const int c = c0 + lane;
       float sum = 0.0f;
-      if (c < H / 8) {
-        const uint4 v = in[c];
-        const uint16_t* hh = reinterpret_cast<const uint16_t*>(&v);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) sum += __bfloat162float(__ushort_as_bfloat16(hh[j]));
-        uint4 sh;
-        sh.x = (uint32_t)hh[0] | ((uint32_t)hh[4] << 16);
-        sh.y = (uint32_t)hh[1] | ((uint32_t)hh[5] << 16);
-        sh.z = (uint32_t)hh[2] | ((uint32_t)hh[6] << 16);
-        sh.w = (uint32_t)hh[3] | ((uint32_t)hh[7] << 16);
-        o[c] = sh;
-      }
+      if (c < H / 8) o[c] = w4_prepare_piece(in[c], true, f16, scale, sum);
 #pragma unroll
       for (int d = 8; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-      if ((lane & 15) == 0 && c < H / 8) xs[(size_t)e * 32 + (c >> 4)] = sum;
+      if ((lane & 15) == 0 && c < H / 8) xs[(size_t)e * W4_XS_STRIDE + (c >> 4)] = sum;
     }
   }
 
@@ -727,7 +734,7 @@ extern "C" int mq_route_small(const void* x, int x_dtype, const void* w, int w_d
                               int64_t T, int64_t H, int64_t E, int64_t K, int renormalize,
                               void* workspace, size_t workspace_bytes, int64_t* ids64, int32_t* ids32,
                               float* weights, int32_t* perm, int32_t* inv, int64_t* offsets64, int32_t* offsets32,
-                              void* xp, float* xs, void* stream) {
+                              void* xp, float* xs, int xp_format, void* stream) {
   using namespace mq;
   if (T < 0 || H <= 0 || E <= 0 || K <= 0) return MQ_ERR_INVALID_ARGUMENT;
   if (!valid_dtype(x_dtype) || !valid_dtype(w_dtype)) return MQ_ERR_INVALID_ARGUMENT;
@@ -736,6 +743,8 @@ extern "C" int mq_route_small(const void* x, int x_dtype, const void* w, int w_d
   // the prepared rows are a bf16 format with 128-k groups, 32 of them at most
   if (xp != nullptr && (x_dtype != MQ_BF16 || H % 128 != 0 || H / 128 > 32)) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (xp != nullptr && T > E) return MQ_ERR_UNSUPPORTED_SHAPE;     // CTA t prepares token t; there are E CTAs
+  if (xp != nullptr && xp_format != 1 && xp_format != 2) return MQ_ERR_INVALID_ARGUMENT;
+  if (xp != nullptr && xp_format == 2 && H / 128 > W4_XS_UNSCALE) return MQ_ERR_UNSUPPORTED_SHAPE;
   if (T == 0) return MQ_OK;
   if (!x || !w || !workspace || !weights || !ids32 || !perm || !inv || (!offsets64 && !offsets32))
     return MQ_ERR_INVALID_ARGUMENT;
@@ -751,7 +760,8 @@ extern "C" int mq_route_small(const void* x, int x_dtype, const void* w, int w_d
     cudaFuncSetAttribute(route_small_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
     launch_after_predecessor(route_small_kernel<EPL>, dim3((unsigned)E), dim3(RSM_THREADS), smem, st,             \
         x, x_dtype, w, w_dtype, bias, (int)T, (int)H, (int)E, (int)K, renormalize, vec_ok, logits, counter, ids32, \
-        ids64, weights, perm, inv, offsets32, offsets64, reinterpret_cast<__nv_bfloat16*>(xp), xs);               \
+        ids64, weights, perm, inv, offsets32, offsets64, reinterpret_cast<__nv_bfloat16*>(xp), xs,                \
+        xp_format == 2 ? 2 : 1);                                                                                  \
   } while (0)
   if (E <= 32) MQ_RSM_LAUNCH(1);
   else if (E <= 64) MQ_RSM_LAUNCH(2);

@@ -376,7 +376,7 @@ void launch_w4_variant(const void* x, W4Proj p0, W4Proj p1, const int32_t* offse
 
 // TMA-staged persistent stream kernel (w4a16_stream.cu): group size 128, N a multiple of 32.
 bool w4a16_stream_covers(int64_t S, int64_t E, int64_t period, int64_t N, int64_t Kd, int64_t group);
-int w4a16_stream(const void* x, const float* xs, bool x_shuffled, const int32_t* perm, int64_t top_k,
+int w4a16_stream(const void* x, const float* xs, int x_format, const int32_t* perm, int64_t top_k,
                  const int32_t* qw0, const void* sc0, const int32_t* qz0, const int32_t* qw1, const void* sc1,
                  const int32_t* qz1, bool swiglu, bool shuffle_out, const int32_t* offsets, int64_t S, int64_t E,
                  int64_t period, int64_t N, int64_t Kd, void* out, int32_t* d_status, cudaStream_t st);
@@ -386,7 +386,7 @@ namespace {
 int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* offsets, int64_t S, int64_t E,
               int64_t period, int64_t N, int64_t Kd, int64_t group, void* out, cudaStream_t st,
               const int32_t* perm = nullptr, int64_t top_k = 1, int32_t* d_status = nullptr,
-              const float* xs = nullptr, bool x_shuffled = false, bool shuffle_out = false, bool want_stream = false) {
+              const float* xs = nullptr, int x_format = 0, bool shuffle_out = false, bool want_stream = false) {
   if (S < 0 || E <= 0 || N <= 0 || Kd <= 0 || group <= 0) return MQ_ERR_INVALID_ARGUMENT;
   if (period <= 0 || period > E) return MQ_ERR_INVALID_ARGUMENT;
   if (group % 32 != 0 || Kd % group != 0 || N % 8 != 0 || E > 65535) return MQ_ERR_UNSUPPORTED_SHAPE;
@@ -401,10 +401,10 @@ int launch_w4(const void* x, W4Proj p0, W4Proj p1, bool swiglu, const int32_t* o
   // no K split).  The prepared-activation entry points ask for the stream kernel explicitly.
   const bool stream = want_stream || (swiglu && S >= 32);
   if (stream && w4a16_stream_covers(S, E, period, N, Kd, group))
-    return w4a16_stream(x, xs, x_shuffled, perm, top_k, p0.qw, p0.sc, p0.qz, p1.qw, p1.sc, p1.qz, swiglu, shuffle_out,
+    return w4a16_stream(x, xs, x_format, perm, top_k, p0.qw, p0.sc, p0.qz, p1.qw, p1.sc, p1.qz, swiglu, shuffle_out,
                         offsets, S, E, period, N, Kd, out, d_status, st);
   // the fallback kernel wants expert-sorted rows in natural order
-  if (perm != nullptr || x_shuffled || shuffle_out) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (perm != nullptr || x_format != 0 || shuffle_out) return MQ_ERR_UNSUPPORTED_SHAPE;
   // few rows in total (a handful of experts hit): split K across the warps of a CTA to get enough CTAs;
   // otherwise every warp streams the whole K of its own column tile
   bool split = S <= 32;
@@ -443,7 +443,7 @@ extern "C" int mq_w4a16_grouped_swiglu(const void* x,
 }
 
 /* Prepared-activation forms: see include/mqmoe.h. */
-extern "C" int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shuffled, const int32_t* perm,
+extern "C" int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_format, const int32_t* perm,
                                       int64_t top_k, const int32_t* qweight_gate, const void* scales_gate, const int32_t* qzeros_gate,
                                       const int32_t* qweight_up, const void* scales_up, const int32_t* qzeros_up,
                                       const int32_t* offsets, int64_t S, int64_t E, int64_t weight_period, int64_t I,
@@ -452,18 +452,18 @@ extern "C" int mq_w4a16_stream_swiglu(const void* xp, const float* xs, int x_shu
   mq::W4Proj pg{qweight_gate, reinterpret_cast<const __nv_bfloat16*>(scales_gate), qzeros_gate};
   mq::W4Proj pu{qweight_up, reinterpret_cast<const __nv_bfloat16*>(scales_up), qzeros_up};
   if (!mq::w4a16_stream_covers(S, E, weight_period, I, H, group_size)) return MQ_ERR_UNSUPPORTED_SHAPE;
-  if (perm != nullptr && top_k <= 0) return MQ_ERR_INVALID_ARGUMENT;
+  if ((perm != nullptr && top_k <= 0) || x_format < 0 || x_format > 2) return MQ_ERR_INVALID_ARGUMENT;
   return mq::launch_w4(xp, pg, pu, true, offsets, S, E, weight_period, I, H, group_size, h,
                        reinterpret_cast<cudaStream_t>(stream), perm, perm != nullptr ? top_k : 1, d_status, xs,
-                       x_shuffled != 0, shuffle_out != 0, true);
+                       x_format, shuffle_out != 0, true);
 }
 
-extern "C" int mq_w4a16_stream_gemm(const void* xp, const float* xs, int x_shuffled, const int32_t* qweight,
+extern "C" int mq_w4a16_stream_gemm(const void* xp, const float* xs, int x_format, const int32_t* qweight,
                                     const void* scales, const int32_t* qzeros, const int32_t* offsets, int64_t S,
                                     int64_t E, int64_t weight_period, int64_t N, int64_t Kd, int64_t group_size,
                                     void* out, int32_t* d_status, void* stream) {
   mq::W4Proj p{qweight, reinterpret_cast<const __nv_bfloat16*>(scales), qzeros};
   if (!mq::w4a16_stream_covers(S, E, weight_period, N, Kd, group_size)) return MQ_ERR_UNSUPPORTED_SHAPE;
   return mq::launch_w4(xp, p, p, false, offsets, S, E, weight_period, N, Kd, group_size, out,
-                       reinterpret_cast<cudaStream_t>(stream), nullptr, 1, d_status, xs, x_shuffled != 0, false, true);
+                       reinterpret_cast<cudaStream_t>(stream), nullptr, 1, d_status, xs, x_format, false, true);
 }

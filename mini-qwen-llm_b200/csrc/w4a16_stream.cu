@@ -128,13 +128,43 @@ __device__ __forceinline__ uint32_t ws_centered_pair(uint32_t w, int p) {
   asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(c) : "r"(v), "r"(0x3F803F80u), "r"(0xC308C308u));
   return c;
 }
+// The four pairs of a word at once, pair p = {q[p] - 8, q[p+4] - 8}.  bf16: one shift and one logic op per pair
+// (seven integer instructions a word).  fp16 has ten mantissa bits, so a nibble can also be picked up where it
+// sits four bits higher: (w & 0x00F000F0) | 0x6400 is the pair {1024 + 16 q[1], 1024 + 16 q[5]}, and one packed
+// FMA (x 1/16, - 72) re-centres it exactly; a word then costs one shift and four logic ops.
+template <bool F16>
+__device__ __forceinline__ void ws_dequant_word(uint32_t w, uint32_t (&d)[4]) {
+  if (!F16) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) d[p] = ws_centered_pair(w, p);
+  } else {
+    const uint32_t w8 = w >> 8;
+    uint32_t t0, t1, t2, t3;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t0) : "r"(w), "r"(0x000F000Fu), "r"(0x64006400u));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t1) : "r"(w), "r"(0x00F000F0u), "r"(0x64006400u));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t2) : "r"(w8), "r"(0x000F000Fu), "r"(0x64006400u));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t3) : "r"(w8), "r"(0x00F000F0u), "r"(0x64006400u));
+    // (1024 + q) - 1032 and (1024 + 16 q) / 16 - 72, both exact in fp16
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d[0]) : "r"(t0), "r"(0x3C003C00u), "r"(0xE408E408u));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d[1]) : "r"(t1), "r"(0x2C002C00u), "r"(0xD480D480u));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d[2]) : "r"(t2), "r"(0x3C003C00u), "r"(0xE408E408u));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d[3]) : "r"(t3), "r"(0x2C002C00u), "r"(0xD480D480u));
+  }
+}
+template <bool F16>
 __device__ __forceinline__ void ws_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
   // not volatile: the accumulator operands carry every dependence, and the scheduler may then interleave
   // the independent accumulator chains of a step
-  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  if (F16) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
 }
 __device__ __forceinline__ uint4 ws_ldg128(const void* p) {
   uint4 v;
@@ -222,18 +252,19 @@ __device__ __forceinline__ float ws_swiglu(float g, float u) {
   return sb * ub;
 }
 
+template <bool F16>
 __device__ __forceinline__ void ws_step(WsStream& a, const uint4& wv, const uint32_t (&b)[4]) {
   const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
   uint32_t d[4][4];
 #pragma unroll
-  for (int c = 0; c < 4; ++c)
-#pragma unroll
-    for (int p = 0; p < 4; ++p) d[c][p] = ws_centered_pair(w[c], p);
+  for (int c = 0; c < 4; ++c) ws_dequant_word<F16>(w[c], d[c]);
   // the two accumulators alternate, so that an MMA never follows the one it depends on
 #pragma unroll
-  for (int m = 0; m < 2; ++m) ws_mma(a.grp[m], d[2 * m][0], d[2 * m + 1][0], d[2 * m][1], d[2 * m + 1][1], b[0], b[1]);
+  for (int m = 0; m < 2; ++m)
+    ws_mma<F16>(a.grp[m], d[2 * m][0], d[2 * m + 1][0], d[2 * m][1], d[2 * m + 1][1], b[0], b[1]);
 #pragma unroll
-  for (int m = 0; m < 2; ++m) ws_mma(a.grp[m], d[2 * m][2], d[2 * m + 1][2], d[2 * m][3], d[2 * m + 1][3], b[2], b[3]);
+  for (int m = 0; m < 2; ++m)
+    ws_mma<F16>(a.grp[m], d[2 * m][2], d[2 * m + 1][2], d[2 * m][3], d[2 * m + 1][3], b[2], b[3]);
 }
 
 // An item of work.
@@ -303,7 +334,9 @@ __device__ void ws_build_item_table(const int32_t* __restrict__ offsets, int E, 
 // XSHUF: the activations already have the k order 0,4,1,5,2,6,3,7 inside every 8 (mq_w4a16_tc_prep, or the
 //        shuffled output of the SwiGLU variant); otherwise the order is made with four byte permutes per step.
 // XSUM:  the group sums come from P.xs; otherwise from one more MMA pair per step against a tile of ones.
-template <bool SWIGLU, bool XSHUF, bool XSUM>
+// F16:   the prepared rows are fp16, each scaled by its own power of two whose inverse sits in slot 31 of the row's
+//        sums (w4_prep.cuh); needs XSHUF and XSUM.
+template <bool SWIGLU, bool XSHUF, bool XSUM, bool F16>
 __global__ void __launch_bounds__(WS_THREADS, 1)
 w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                     const WsParams P) {
@@ -480,11 +513,16 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     // its results are not stored)
     const float* xsrow = nullptr;
     int xs_delta = 0;
+    float unscale[2] = {1.0f, 1.0f};                          // F16: 2^-e of rows 2kq and 2kq+1, used when the item ends
     if (XSUM) {
       const WsListed& lc = list[q % WS_LIST];
       const int s0 = lc.src[2 * kq], s1 = lc.src[2 * kq + 1];
       xsrow = P.xs + (size_t)s0 * 32;
       xs_delta = (s1 - s0) * 32;
+      if (F16) {
+        unscale[0] = xsrow[31];
+        unscale[1] = xsrow[xs_delta + 31];
+      }
     }
 
     WsStream st[NS];
@@ -541,17 +579,17 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
               b[3] = ws_prmt(xv.y, xv.w, 0x7632);
             }
             if (!XSUM) {
-              ws_mma(xs, BF16_ONES2, BF16_ONES2, BF16_ONES2, BF16_ONES2, b[0], b[1]);
-              ws_mma(xs, BF16_ONES2, BF16_ONES2, BF16_ONES2, BF16_ONES2, b[2], b[3]);
+              ws_mma<false>(xs, BF16_ONES2, BF16_ONES2, BF16_ONES2, BF16_ONES2, b[0], b[1]);
+              ws_mma<false>(xs, BF16_ONES2, BF16_ONES2, BF16_ONES2, BF16_ONES2, b[2], b[3]);
             }
             {
               const uint4 wv = *reinterpret_cast<const uint4*>(rows + (s >> 1) * 1024 + (s & 1) * 128 + piece[s & 1]);
-              ws_step(st[0], wv, b);
+              ws_step<F16>(st[0], wv, b);
             }
             if (SWIGLU) {
               const uint4 wv =
                   *reinterpret_cast<const uint4*>(rows + (s >> 1) * 1024 + (s & 1) * 128 + piece[s & 1] + proj_bytes);
-              ws_step(st[NS - 1], wv, b);
+              ws_step<F16>(st[NS - 1], wv, b);
             }
           }
 #pragma unroll
@@ -576,6 +614,12 @@ w4a16_stream_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
       }
       ++nstage;
       if (++stage == P.nst) { stage = 0; phase ^= 1u; }
+    }
+    if (F16) {                                                 // back to the rows' own scale (a power of two: exact)
+#pragma unroll
+      for (int q2 = 0; q2 < NS; ++q2)
+#pragma unroll
+        for (int idx = 0; idx < 8; ++idx) st[q2].master[idx >> 2][idx & 3] *= unscale[idx & 1];
     }
     Pending cur_f;
     cur_f.row0 = it.row0; cur_f.rows = it.rows; cur_f.col = col; cur_f.q = q;
@@ -680,11 +724,12 @@ bool w4a16_stream_covers(int64_t S, int64_t E, int64_t period, int64_t N, int64_
 }
 
 // x: activations; perm != nullptr gathers row p of the sorted order from x[perm[p] / top_k].
-// x_shuffled: x already has the k order 0,4,1,5,2,6,3,7 inside every 8; xs (optional): group sums of the rows
+// x_format: 0 = bf16 rows in natural k order; 1 = bf16 rows with the k order 0,4,1,5,2,6,3,7 inside every 8;
+// 2 = that order in fp16, every row scaled by its power of two (needs xs); xs (optional): group sums of the rows
 // of x, [rows, 32] fp32 (both are what mq_w4a16_tc_prep writes).  shuffle_out: write the output columns in
 // that same order (it is then the prepared input of the next projection).
 // qw/sc/qz of the projection(s) in the checkpoint layout, `period` weight sets.
-int w4a16_stream(const void* x, const float* xs, bool x_shuffled, const int32_t* perm, int64_t top_k,
+int w4a16_stream(const void* x, const float* xs, int x_format, const int32_t* perm, int64_t top_k,
                  const int32_t* qw0, const void* sc0, const int32_t* qz0, const int32_t* qw1, const void* sc1,
                  const int32_t* qz1, bool swiglu, bool shuffle_out, const int32_t* offsets, int64_t S, int64_t E,
                  int64_t period, int64_t N, int64_t Kd, void* out, int32_t* d_status, cudaStream_t st) {
@@ -745,22 +790,27 @@ int w4a16_stream(const void* x, const float* xs, bool x_shuffled, const int32_t*
     return MQ_ERR_DRIVER_ENTRY;
   const int grid = ws_sm_count();
   const bool xsum = xs != nullptr;
-#define MQ_WS_LAUNCH(SW, XSH, XSU)                                                                                 \
+#define MQ_WS_LAUNCH(SW, XSH, XSU, F16)                                                                            \
   do {                                                                                                             \
-    static const int smem = ws_dynamic_smem_bytes(reinterpret_cast<const void*>(w4a16_stream_kernel<SW, XSH, XSU>)); \
+    static const int smem =                                                                                        \
+        ws_dynamic_smem_bytes(reinterpret_cast<const void*>(w4a16_stream_kernel<SW, XSH, XSU, F16>));              \
     if (smem <= 0) return MQ_ERR_LAUNCH_FAILED;                                                                    \
-    launch_after_predecessor(w4a16_stream_kernel<SW, XSH, XSU>, dim3(grid), dim3(WS_THREADS), (size_t)smem, st,    \
-                             map0, map1, P);                                                                       \
+    launch_after_predecessor(w4a16_stream_kernel<SW, XSH, XSU, F16>, dim3(grid), dim3(WS_THREADS), (size_t)smem,   \
+                             st, map0, map1, P);                                                                   \
   } while (0)
+  const bool x_shuffled = x_format != 0;
+  if (x_format == 2 && (!xsum || G > 31)) return MQ_ERR_INVALID_ARGUMENT;       // fp16 rows come with their sums table
   if (swiglu) {
-    if (x_shuffled && xsum) MQ_WS_LAUNCH(true, true, true);
-    else if (x_shuffled) MQ_WS_LAUNCH(true, true, false);
-    else if (!xsum) MQ_WS_LAUNCH(true, false, false);
+    if (x_format == 2) MQ_WS_LAUNCH(true, true, true, true);
+    else if (x_shuffled && xsum) MQ_WS_LAUNCH(true, true, true, false);
+    else if (x_shuffled) MQ_WS_LAUNCH(true, true, false, false);
+    else if (!xsum) MQ_WS_LAUNCH(true, false, false, false);
     else return MQ_ERR_INVALID_ARGUMENT;             // sums without the shuffled rows: not a combination any caller makes
   } else {
-    if (x_shuffled && xsum) MQ_WS_LAUNCH(false, true, true);
-    else if (x_shuffled) MQ_WS_LAUNCH(false, true, false);
-    else if (!xsum) MQ_WS_LAUNCH(false, false, false);
+    if (x_format == 2) MQ_WS_LAUNCH(false, true, true, true);
+    else if (x_shuffled && xsum) MQ_WS_LAUNCH(false, true, true, false);
+    else if (x_shuffled) MQ_WS_LAUNCH(false, true, false, false);
+    else if (!xsum) MQ_WS_LAUNCH(false, false, false, false);
     else return MQ_ERR_INVALID_ARGUMENT;
   }
 #undef MQ_WS_LAUNCH

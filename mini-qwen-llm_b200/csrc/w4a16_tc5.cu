@@ -35,6 +35,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "w4_prep.cuh"
 
 namespace mq {
 namespace {
@@ -454,31 +455,30 @@ w4a16_tc5_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 // src(r) = perm[r] / top_k when perm is given (the expert-sorted order), else r.  One warp per row.
 __global__ void __launch_bounds__(256)
 w4_prep_rows(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ perm, int top_k, int S, int Kd,
-             int shuffle, __nv_bfloat16* __restrict__ xp, float* __restrict__ xs) {
+             int mode, __nv_bfloat16* __restrict__ xp, float* __restrict__ xs) {
   const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= S) return;
   const int lane = threadIdx.x & 31;
   const size_t src = perm != nullptr ? (size_t)(perm[r] / top_k) : (size_t)r;
   const uint4* in = reinterpret_cast<const uint4*>(x + src * Kd);
   uint4* o = xp != nullptr ? reinterpret_cast<uint4*>(xp + (size_t)r * Kd) : nullptr;
+  const bool f16 = mode == 2;
+  float scale = 1.0f;
+  if (f16) {                                       // the row's largest magnitude decides its power of two
+    float amax = 0.0f;
+    for (int c = lane; c < Kd / 8; c += 32) amax = fmaxf(amax, w4_piece_amax(in[c]));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    const int e = w4_row_exponent(amax);
+    scale = w4_pow2(e);
+    if (lane == 0) xs[(size_t)r * W_XS_STRIDE + W4_XS_UNSCALE] = w4_pow2(-e);
+  }
   for (int c0 = 0; c0 < Kd / 8; c0 += 32) {      // 16-byte pieces; a group of 128 k is 16 pieces = half a warp
     const int c = c0 + lane;
     float sum = 0.0f;
     if (c < Kd / 8) {
-      const uint4 v = in[c];
-      const uint16_t* h = reinterpret_cast<const uint16_t*>(&v);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) sum += __bfloat162float(__ushort_as_bfloat16(h[j]));
-      if (o != nullptr) {
-        uint4 w = v;
-        if (shuffle) {
-          w.x = (uint32_t)h[0] | ((uint32_t)h[4] << 16);
-          w.y = (uint32_t)h[1] | ((uint32_t)h[5] << 16);
-          w.z = (uint32_t)h[2] | ((uint32_t)h[6] << 16);
-          w.w = (uint32_t)h[3] | ((uint32_t)h[7] << 16);
-        }
-        o[c] = w;
-      }
+      const uint4 w = w4_prepare_piece(in[c], mode != 0, f16, scale, sum);
+      if (o != nullptr) o[c] = w;
     }
 #pragma unroll
     for (int d = 8; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
@@ -538,7 +538,9 @@ extern "C" int mq_w4a16_tc_prep(const void* x, const int32_t* perm, int64_t top_
                                 int shuffle, void* xp, float* xs, void* stream) {
   using namespace mq;
   if (S < 0 || Kd <= 0 || (perm != nullptr && top_k <= 0)) return MQ_ERR_INVALID_ARGUMENT;
+  if (shuffle < 0 || shuffle > 2) return MQ_ERR_INVALID_ARGUMENT;
   if (Kd % 128 != 0 || Kd / 128 > W_XS_STRIDE || S >= ((int64_t)1 << 30)) return MQ_ERR_UNSUPPORTED_SHAPE;
+  if (shuffle == 2 && Kd / 128 > W4_XS_UNSCALE) return MQ_ERR_UNSUPPORTED_SHAPE;   // the last slot carries 2^-e
   if (S == 0) return MQ_OK;
   if (!x || !xs || !aligned16(x) || (xp && !aligned16(xp))) return MQ_ERR_INVALID_ARGUMENT;
   w4_prep_rows<<<(unsigned)((S + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(

@@ -27,7 +27,7 @@ PROTOTYPES = {
     "mq_router_topk": (c_int, [_P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, c_size_t, _P, _P, _P, _P]),
     "mq_router_topk_static": (c_int, [_P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, _P, _P, _P]),
     "mq_route_small_workspace_bytes": (c_size_t, [_L, _L]),
-    "mq_route_small": (c_int, [_P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, c_size_t, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "mq_route_small": (c_int, [_P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, c_size_t, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P]),
     "mq_permute_workspace_bytes": (c_size_t, [_L, _L]),
     "mq_permute_plan": (c_int, [_P, _I, _L, _L, _L, _P, _P, _P, _P, _P, c_size_t, _P]),
     "mq_gather_rows": (c_int, [_P, _I, _P, _L, _L, _L, _P, _P]),

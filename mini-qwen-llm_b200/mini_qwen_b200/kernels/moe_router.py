@@ -72,8 +72,9 @@ def moe_route_small(hidden_states: torch.Tensor, router_weight: torch.Tensor, to
     for at most 64 tokens: what ``moe_router`` + ``moe_permute_plan`` (+ ``w4a16_tc_prep``) do in three or four.
 
     Returns ``(ids32 [T,K], weights fp32 [T,K], perm int32 [S], inv int32 [S], offsets32 int32 [E+1], xp, xs)``;
-    ``xp`` (bf16 [T,H], token rows in the k order the W4A16 kernels multiply in) and ``xs`` (fp32 [T,32], their
-    sums over every 128 k) are None unless ``prepare``.  ``workspace``: a tensor from
+    ``xp`` ([T,H], token rows in the k order the W4A16 kernels multiply in) and ``xs`` (fp32 [T,32], their
+    sums over every 128 k) are None unless ``prepare``: True or "bf16" for bf16 rows, "f16" for fp16 rows scaled
+    by their power of two (the stream kernels' faster format, H <= 3968).  ``workspace``: a tensor from
     :func:`route_small_workspace` to reuse across calls (a fresh one is made otherwise)."""
     _cabi.require_cuda(hidden_states, router_weight, bias)
     T, H = hidden_states.shape
@@ -94,14 +95,16 @@ def moe_route_small(hidden_states: torch.Tensor, router_weight: torch.Tensor, to
     inv = torch.empty(S, dtype=torch.int32, device=dev)
     off32 = torch.empty(E + 1, dtype=torch.int32, device=dev)
     xp = xs = None
+    fmt = 0
     if prepare:
-        assert x.dtype == torch.bfloat16 and H % 128 == 0 and H <= 4096
-        xp = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        fmt = 2 if prepare == "f16" else 1
+        assert x.dtype == torch.bfloat16 and H % 128 == 0 and H <= (3968 if fmt == 2 else 4096)
+        xp = torch.empty(T, H, dtype=torch.float16 if fmt == 2 else torch.bfloat16, device=dev)
         xs = torch.empty(T, 32, dtype=torch.float32, device=dev)
     rc = lib.mq_route_small(_cabi.ptr(x), _cabi.dtype_code(x), _cabi.ptr(w), _cabi.dtype_code(w), _cabi.ptr(bias),
                             T, H, E, top_k, int(renormalize), _cabi.ptr(ws), ws_bytes, None, _cabi.ptr(ids32),
                             _cabi.ptr(wts), _cabi.ptr(perm), _cabi.ptr(inv), None, _cabi.ptr(off32),
-                            _cabi.ptr(xp), _cabi.ptr(xs), _cabi.stream_ptr(dev))
+                            _cabi.ptr(xp), _cabi.ptr(xs), fmt, _cabi.stream_ptr(dev))
     _cabi.check(rc, "mq_route_small")
     _cabi.count_launches(1)
     return ids32, wts, perm, inv, off32, xp, xs

@@ -26,11 +26,11 @@ def _offsets32(expert_offsets: torch.Tensor) -> torch.Tensor:
     return off.contiguous()
 
 
-def _check_w4(x, qweight, scales, qzeros, group_size, E):
+def _check_w4(x, qweight, scales, qzeros, group_size, E, prepared_f16=False):
     assert x.is_cuda and qweight.is_cuda, "w4a16 kernels run on CUDA tensors only"
     assert qweight.is_contiguous() and scales.is_contiguous() and qzeros.is_contiguous(), \
         "qweight, scales and qzeros must be contiguous (the kernels index them as dense expert-major stacks)"
-    assert x.dtype == torch.bfloat16, "activations must be bfloat16"
+    assert x.dtype == (torch.float16 if prepared_f16 else torch.bfloat16), "activations must be bfloat16"
     assert qweight.dtype == torch.int32 and qzeros.dtype == torch.int32 and scales.dtype == torch.bfloat16
     K = x.shape[-1]
     N = qweight.shape[-1]
@@ -119,10 +119,13 @@ def w4a16_stream_swiglu(xp, xs, gate, up, expert_offsets, group_size: int = 128,
     """Fused gate/up + SwiGLU on prepared activations (``w4a16_tc_prep``): ``xp`` the expert-sorted rows in the
     shuffled k order, ``xs`` their group sums (or None).  With ``shuffle_out`` the result's columns are in the
     shuffled order, ready for :func:`w4a16_stream_gemm` with ``x_shuffled=True``.  With ``perm`` (int32 [S]),
-    ``xp``/``xs`` hold one row per token and sorted row p is row ``perm[p] // top_k`` (``moe_route_small``)."""
+    ``xp``/``xs`` hold one row per token and sorted row p is row ``perm[p] // top_k`` (``moe_route_small``).
+    ``xp`` of dtype float16 is the row-scaled fp16 format (``w4a16_tc_prep(..., f16=True)``)."""
     E = gate[0].shape[0]
-    K, N = _check_w4(xp, *gate, group_size, E)
-    _check_w4(xp, *up, group_size, E)
+    f16 = xp.dtype == torch.float16
+    assert not f16 or (x_shuffled and xs is not None)
+    K, N = _check_w4(xp, *gate, group_size, E, f16)
+    _check_w4(xp, *up, group_size, E, f16)
     expert_offsets = _offsets32(expert_offsets)
     groups = expert_offsets.numel() - 1
     assert xp.is_contiguous() and (xs is None or (xs.is_contiguous() and xs.dtype == torch.float32))
@@ -131,7 +134,7 @@ def w4a16_stream_swiglu(xp, xs, gate, up, expert_offsets, group_size: int = 128,
         assert perm.dtype == torch.int32 and perm.is_contiguous() and top_k >= 1
     h = torch.empty(S, N, dtype=torch.bfloat16, device=xp.device)
     rc = _cabi.load().mq_w4a16_stream_swiglu(
-        _cabi.ptr(xp), _cabi.ptr(xs), 1 if x_shuffled else 0, _cabi.ptr(perm), top_k,
+        _cabi.ptr(xp), _cabi.ptr(xs), 2 if f16 else (1 if x_shuffled else 0), _cabi.ptr(perm), top_k,
         _cabi.ptr(gate[0]), _cabi.ptr(gate[1]), _cabi.ptr(gate[2]),
         _cabi.ptr(up[0]), _cabi.ptr(up[1]), _cabi.ptr(up[2]), _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size,
         1 if shuffle_out else 0, _cabi.ptr(h), _cabi.ptr(status), _cabi.stream_ptr(xp.device))
@@ -144,7 +147,9 @@ def w4a16_stream_gemm(xp, xs, qweight, scales, qzeros, expert_offsets, group_siz
                       status: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """One W4A16 projection per group on prepared activations; natural column order."""
     E = qweight.shape[0]
-    K, N = _check_w4(xp, qweight, scales, qzeros, group_size, E)
+    f16 = xp.dtype == torch.float16
+    assert not f16 or (x_shuffled and xs is not None)
+    K, N = _check_w4(xp, qweight, scales, qzeros, group_size, E, f16)
     expert_offsets = _offsets32(expert_offsets)
     groups = expert_offsets.numel() - 1
     assert xp.is_contiguous() and (xs is None or (xs.is_contiguous() and xs.dtype == torch.float32))
@@ -153,7 +158,8 @@ def w4a16_stream_gemm(xp, xs, qweight, scales, qzeros, expert_offsets, group_siz
         out = torch.empty(S, N, dtype=torch.bfloat16, device=xp.device)
     assert out.is_contiguous() and tuple(out.shape) == (S, N) and out.dtype == torch.bfloat16
     rc = _cabi.load().mq_w4a16_stream_gemm(
-        _cabi.ptr(xp), _cabi.ptr(xs), 1 if x_shuffled else 0, _cabi.ptr(qweight), _cabi.ptr(scales), _cabi.ptr(qzeros),
+        _cabi.ptr(xp), _cabi.ptr(xs), 2 if f16 else (1 if x_shuffled else 0), _cabi.ptr(qweight), _cabi.ptr(scales),
+        _cabi.ptr(qzeros),
         _cabi.ptr(expert_offsets), S, groups, E, N, K, group_size, _cabi.ptr(out), _cabi.ptr(status),
         _cabi.stream_ptr(xp.device))
     _cabi.check(rc, "mq_w4a16_stream_gemm")
@@ -169,17 +175,22 @@ def w4a16_tc_supported(hidden: int, out_features: int, group_size: int) -> bool:
 
 
 def w4a16_tc_prep(x: torch.Tensor, perm: torch.Tensor | None = None, top_k: int = 1, shuffle: bool = True,
-                  want_rows: bool = True):
-    """Activations for the tensor-memory kernels: (xp, xs).  xp [S, K] = the (optionally gathered) rows with
-    the k order 0,4,1,5,2,6,3,7 inside every 8; xs fp32 [S, 32] = per-row sums over every 128 k."""
+                  want_rows: bool = True, f16: bool = False):
+    """Prepared activations for the stream and tensor-memory kernels: (xp, xs).  xp [S, K] = the (optionally
+    gathered) rows with the k order 0,4,1,5,2,6,3,7 inside every 8; xs fp32 [S, 32] = per-row sums over every
+    128 k.  ``f16`` (stream kernels only, K <= 3968): xp is float16, every row scaled by the power of two that
+    puts its largest magnitude into [2^14, 2^15); xs holds the sums of the scaled values and, in column 31, the
+    inverse of the row's factor."""
     assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2
     x = x.contiguous()
     S = perm.numel() if perm is not None else x.shape[0]
     K = x.shape[1]
-    xp = torch.empty(S, K, dtype=torch.bfloat16, device=x.device) if want_rows else None
+    assert not f16 or (shuffle and K <= 3968)
+    xp = torch.empty(S, K, dtype=torch.float16 if f16 else torch.bfloat16, device=x.device) if want_rows else None
     xs = torch.empty(S, 32, dtype=torch.float32, device=x.device)
     rc = _cabi.load().mq_w4a16_tc_prep(_cabi.ptr(x), _cabi.ptr(perm) if perm is not None else None, top_k, S, K,
-                                       1 if shuffle else 0, _cabi.ptr(xp) if want_rows else None, _cabi.ptr(xs),
+                                       2 if f16 else (1 if shuffle else 0), _cabi.ptr(xp) if want_rows else None,
+                                       _cabi.ptr(xs),
                                        _cabi.stream_ptr(x.device))
     _cabi.check(rc, "mq_w4a16_tc_prep")
     _cabi.count_launches(1 if S else 0)

@@ -371,6 +371,12 @@ def test_fused_small_batch_routing_equals_the_separate_kernels_and_the_oracle(T,
         if prepare:
             xp2, xs2 = w4a16_tc_prep(x.to(DEV))          # per token, no gather
             assert torch.equal(xp, xp2) and torch.equal(xs[:, : H // 128], xs2[:, : H // 128])
+            # ... and in the fp16 format (rows scaled by their power of two, its inverse in column 31)
+            *_, xp16, xs16 = moe_route_small(x.to(DEV), w.to(DEV), K, bias=None if bias is None else bias.to(DEV),
+                                             renormalize=renorm, prepare="f16", workspace=ws)
+            xp3, xs3 = w4a16_tc_prep(x.to(DEV), f16=True)
+            assert xp16.dtype == torch.float16 and torch.equal(xp16, xp3)
+            assert torch.equal(xs16[:, : H // 128], xs3[:, : H // 128]) and torch.equal(xs16[:, 31], xs3[:, 31])
     # the separate launches give the same weights bit for bit or within an fp32 rounding of the logits
     ids_b, w_b, ids32_b = moe_router(x.to(DEV), w.to(DEV), K, bias=None if bias is None else bias.to(DEV),
                                      renormalize=renorm, return_int32_ids=True)

@@ -59,8 +59,13 @@ def test_stream_kernel_gate_up_and_down_match_the_oracle(T, H, E, K, I, skew):
     h64 = cases.w4_grouped_reference(rows.cpu(), (cpu_set(lay.gate), cpu_set(lay.up)), off, torch.float64)
 
     xp, xs = w4a16_tc_prep(x, perm, K)
+    xp16, xs16 = w4a16_tc_prep(x, perm, K, f16=True)             # rows scaled by their power of two, fp16
+    x16_tok, xs16_tok = w4a16_tc_prep(x, f16=True)               # the same per token, gathered inside the kernel
     pos = kperm_index(I).to(DEV)
     variants = {
+        "fp16 rows": w4a16_stream_swiglu(xp16, xs16, gate, up, off32, shuffle_out=False, status=status),
+        "fp16 rows, gathered through perm": w4a16_stream_swiglu(x16_tok, xs16_tok, gate, up, off32, shuffle_out=False,
+                                                                status=status, perm=perm, top_k=K),
         "prepared, sums given, shuffled out": w4a16_stream_swiglu(xp, xs, gate, up, off32, status=status)[:, pos],
         "prepared, sums given": w4a16_stream_swiglu(xp, xs, gate, up, off32, shuffle_out=False, status=status),
         "prepared, sums by MMA": w4a16_stream_swiglu(xp, None, gate, up, off32, shuffle_out=False, status=status),
@@ -75,6 +80,17 @@ def test_stream_kernel_gate_up_and_down_match_the_oracle(T, H, E, K, I, skew):
     # the same arithmetic in every variant: identical bits
     first = variants["prepared, sums given"]
     assert torch.equal(variants["prepared, sums given, shuffled out"], first)
+    assert torch.equal(variants["fp16 rows"], variants["fp16 rows, gathered through perm"])
+    # the scaling by a power of two is exact: N(0,1) rows hold no element 2^28 times smaller than their largest,
+    # so the fp16 format gives the bf16 format's bits
+    assert torch.equal(variants["fp16 rows"], first)
+    # the format itself: the stored values times the inverse factor are the bf16 values, the factor puts the row's
+    # largest magnitude into [2^14, 2^15)
+    unscale = xs16[:, 31:32]
+    assert torch.equal((xp16.float() * unscale).to(torch.bfloat16), xp)
+    amax = xp16.float().abs().amax(dim=1)
+    assert bool(((amax >= 2.0 ** 14) & (amax < 2.0 ** 15)).all())
+    torch.testing.assert_close(xs16[:, : H // 128] * unscale, xs[:, : H // 128], rtol=1e-6, atol=0)
     assert status.item() == 0
 
     # down projection on the gate/up result (natural order, shuffled, shuffled with sums)
