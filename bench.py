@@ -652,11 +652,14 @@ def run_c5(args):
     T = B // world
     blocks = [w4_block(dev, 200 + L, rank, world, hn.group, max_tokens=T, w4_kernel=args.w4_kernel) for L in range(LAYERS)]
 
-    from mini_qwen_b200.synthetic import rms_norm_weightless
+    # between the layers: an RMS norm with a weight of ones (the stack has no attention and no learnt norms; without
+    # it SwiGLU's quadratic growth overflows within a few layers), on the library's own norm kernel
+    from mini_qwen_b200.model.layers import rms_norm
+    ones = torch.ones(H, dtype=torch.bfloat16, device=dev)
 
     def model(x):
         for i, blk in enumerate(blocks):
-            x = blk(rms_norm_weightless(x) if i else x)
+            x = blk(rms_norm(x, ones, 1e-6) if i else x)
         return x
     x_all = torch.randn(B, H, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
     x_cpu = x_all[rank * T:(rank + 1) * T].contiguous()

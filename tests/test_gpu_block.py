@@ -117,12 +117,21 @@ def test_block_config3_w4a16_decode(T):
         print(f"\nC3 T={T} {kernel}: outside rtol/atol {shares[0]:.4%} (reference vs exact sums {shares[1]:.4%}); "
               f"max distance from exact sums {shares[2]:.4g} (reference {shares[3]:.4g})")
         assert torch.equal(blk(x), got)                     # deterministic across calls
+        if kernel == "stream":
+            got_stream = got
     blk.w4_kernel = "stream"
     # routing by the separate kernels instead of the fused small-batch launch: the same experts; the weights
     # come from logits summed in another order, so the outputs agree to the bar, not to the bit
     blk.fuse_small_batches = False
     cases.w4_output_bar(cpu(blk(x)), ref, ref64)
     blk.fuse_small_batches = True
+    # the fp16 activation format of the stream kernel (rows scaled by their power of two): the same bits
+    blk.w4_rows_f16 = True
+    assert torch.equal(blk(x), got_stream)
+    blk.w4_rows_f16 = False
+    # the layer's residual add inside the combine kernel: the add of two bf16 tensors
+    res = (torch.randn(T, 2048, generator=torch.Generator().manual_seed(T)) * 4).to(torch.bfloat16).to(DEV)
+    assert torch.equal(blk(x, residual=res), res + got_stream)
     blk.check_status()
 
 
