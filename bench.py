@@ -720,8 +720,9 @@ def run_c5(args):
                    "l2": f"a pass streams {LAYERS} different layers ({bytes_gpu / 1e9:.2f} GB per GPU): no weight byte is reused "
                          "from L2 between passes",
                    "parallelism": "single GPU" if world == 1 else
-                   f"expert parallel ep{world}: {E // world} experts per GPU and layer, {T} token(s) per GPU, per-slot dispatch "
-                   "by NVLink stores, expert outputs pulled by the combine kernel, flag barriers between ranks"},
+                   f"expert parallel ep{world}: {E // world} experts per GPU and layer, {T} token(s) per GPU; every rank "
+                   "gathers all tokens over NVLink, routes them, runs its own experts and sends fp32 partial sums to the "
+                   "tokens' owners; two flag barriers between the ranks per layer"},
         "roofline": roofline, "cpu_baseline": cpu_base,
         "e2e": {"value": B * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": out_bytes, "ms_per_step": e2e_ms / args.steps,

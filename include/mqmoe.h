@@ -385,6 +385,35 @@ int mq_ep_combine(const uint64_t* peer_y_ptrs, int dtype, const float* weights, 
                   const int32_t* slot_dst, const void* residual, int64_t T, int64_t K, int64_t H,
                   int64_t cap_rows, void* out, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Expert parallelism for decode batches by replication (no counterpart in the reference).  With a few
+ * tokens per GPU the dispatch / return exchange above is bound by its rank barriers; here every rank
+ * gathers ALL tokens of the step, routes them itself (identical ids, weights and plan on every rank), runs
+ * only its own experts on the slots they own (the grouped calls take an offsets pointer that starts at the
+ * rank's first expert) and sends every token's partial weighted sum to the rank that owns the token.  Two
+ * rank barriers per layer call, inside these kernels.  All ranks must call with the same T.
+ * mq_ep_gather_tokens: x [T,H] of this rank -> rows [rank*T, rank*T+T) of every peer's token buffer
+ *   (peer_token_ptrs: G device addresses of [G*T,H] buffers of `dtype`), then the rank barrier.
+ * mq_ep_send_partials: tokens = G*T; for every token t: the fp32 sum over the slots k with
+ *   topk_ids[t,k] / experts_per_rank == rank of weights[t,k] * float(rows[inv[t*K+k]]), k ascending, stored
+ *   into row (rank*T + t % T) of the fp32 [G*T,H] buffer of rank t / T (peer_partial_ptrs); then the rank
+ *   barrier.  done_counter: one int32, zero before the first call (the kernel leaves it at zero).
+ * mq_ep_sum_partials: out[t,:] = cast(sum over r ascending of partials[r*T + t,:]) for this rank's T tokens;
+ *   residual (optional) as in mq_unpermute_combine_residual.
+ * The barrier is mq_ep_barrier's (same signal arrays and epoch counter, same max_polls, same status bit).
+ * Outputs equal the single-GPU ones up to the order of the fp32 sums.
+ */
+int mq_ep_gather_tokens(const void* x, int dtype, int64_t T, int64_t H, int64_t G, int64_t rank,
+                        const uint64_t* peer_token_ptrs, const uint64_t* peer_signal_ptrs,
+                        int32_t* epoch_counter, int64_t max_polls, int32_t* d_status, void* stream);
+int mq_ep_send_partials(const void* rows, int dtype, const float* weights, const int32_t* topk_ids,
+                        const int32_t* inv, int64_t tokens, int64_t K, int64_t H, int64_t T, int64_t G,
+                        int64_t rank, int64_t experts_per_rank, const uint64_t* peer_partial_ptrs,
+                        int32_t* done_counter, const uint64_t* peer_signal_ptrs, int32_t* epoch_counter,
+                        int64_t max_polls, int32_t* d_status, void* stream);
+int mq_ep_sum_partials(const float* partials, int dtype, const void* residual, int64_t T, int64_t H,
+                       int64_t G, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -54,6 +54,9 @@ PROTOTYPES = {
     "mq_ep_unique_rows": (c_int, [_P, _L, _L, _L, _L, _P, _P]),
     "mq_ep_dispatch_unique": (c_int, [_P, _I, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _P, _P, _P, _L, _P, _P, _P]),
     "mq_ep_combine": (c_int, [_P, _I, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
+    "mq_ep_gather_tokens": (c_int, [_P, _I, _L, _L, _L, _L, _P, _P, _P, _L, _P, _P]),
+    "mq_ep_send_partials": (c_int, [_P, _I, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _P, _P, _P, _P, _L, _P, _P]),
+    "mq_ep_sum_partials": (c_int, [_P, _I, _P, _L, _L, _L, _P, _P]),
 }
 
 _lib = None

@@ -92,6 +92,10 @@ class Qwen3MoEBlock(nn.Module):
         # the fp32 logit sums
         self.fuse_small_batches = True
         self.fuse_max_tokens = 64
+        # expert-parallel W4A16 decode batches (at most 64 tokens over all ranks): "replicate" = every rank holds
+        # all tokens and runs its own experts (two rank barriers per call), "dispatch" = the prefill path
+        self.ep_decode = "replicate"
+        self._decode_mode_used = None
         self._route_ws = None
         self._peer = None
         self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
@@ -243,6 +247,8 @@ class Qwen3MoEBlock(nn.Module):
 
         run = self._stage
         xp_tok = xs_tok = None
+        if self._replicated_decode(st, x2d, T, E, K):
+            return self._forward_replicated(x2d, st, T, K, E, res).reshape(shape)
         if self.fuse_small_batches and 0 < T <= self.fuse_max_tokens and route_small_supported(T, E, K):
             # decode batches: logits, top-k, plan and (one GPU) the W4A16 activation preparation in one launch
             prepare = (self.ep_size == 1 and st["w4"] and x2d.dtype == torch.bfloat16 and self._w4_stream(st)
@@ -361,10 +367,7 @@ class Qwen3MoEBlock(nn.Module):
         if self._peer is not None:
             self._peer.check_status()
 
-    def _forward_peer(self, x2d, st, weights, ids32, perm, inv, off32, T, K, E, res=None):
-        """Expert-parallel path over peer memory: rows go straight from x into the owners' receive
-        buffers and expert outputs are read straight from the owners while combining."""
-        run = self._stage
+    def _ensure_peer(self, x2d, T, K):
         if self._peer is None:
             max_t = self.ep_max_tokens or T
             self._peer = parallel.PeerExchange(self.ep_group, x2d.device, self.ep_size * max_t * K, x2d.shape[1],
@@ -374,6 +377,57 @@ class Qwen3MoEBlock(nn.Module):
         if T > self.ep_max_tokens or x2d.dtype != peer.dtype:
             raise ValueError(f"expert-parallel buffers were sized for {self.ep_max_tokens} tokens of {peer.dtype} per "
                              f"rank; got {T} of {x2d.dtype} (pass ep_max_tokens at construction)")
+        return peer
+
+    def _replicated_decode(self, st, x2d, T, E, K) -> bool:
+        """Decode batches of an expert-parallel W4A16 block go by replication (``ep_decode = "replicate"``): every
+        rank holds all G*T tokens, runs its own experts and sends partial sums; see ``_forward_replicated``."""
+        B = self.ep_size * T
+        return (self.ep_size > 1 and self.ep_mode == "p2p" and self.ep_decode == "replicate" and st["w4"]
+                and x2d.dtype == torch.bfloat16 and self._w4_stream(st) and 0 < B <= self.fuse_max_tokens
+                and B <= E and route_small_supported(B, E, K) and K >= 2)
+
+    def _forward_replicated(self, x2d, st, T, K, E, res=None):
+        """Expert parallelism for decode batches: all-gather the step's tokens (a few rows), route them on every
+        rank (same kernel, same bytes: same plan everywhere), run this rank's experts on the slots they own, send
+        every token's partial weighted sum to the rank that owns the token, add the partial sums up in rank order.
+        Two rank barriers per call instead of four, and each rank streams only its own experts' weights.  Every
+        rank must call with the same number of tokens.  Outputs equal the dispatch path's up to the order of the
+        fp32 sums of the combine."""
+        run = self._stage
+        peer = self._ensure_peer(x2d, T, K)
+        self._decode_mode_used = self._decode_mode_used or "replicate"
+        if self._decode_mode_used != "replicate":
+            raise RuntimeError("this block has run decode batches by dispatch; ep_decode cannot change afterwards")
+        G, el = self.ep_size, E // self.ep_size
+        x_all = run("gather_tokens", peer.gather_tokens, x2d)                        # [G*T, H], barrier inside
+        if self._route_ws is None or self._route_ws.device != x2d.device:
+            self._route_ws = route_small_workspace(E, x2d.device)
+        prepare = "f16" if (self.w4_rows_f16 and x2d.shape[1] <= 3968) else True
+        ids32, weights, perm, inv, off32, xp_tok, xs_tok = run(
+            "route_small", moe_route_small, x_all, self.gate.weight, K, bias=self.router_bias,
+            renormalize=self.norm_topk_prob, prepare=prepare, workspace=self._route_ws)
+        # this rank's experts: the offsets from its first expert on; rows keep their positions in the sorted order
+        off_local = off32[self.ep_rank * el: self.ep_rank * el + el + 1]
+        status = self._status_word(x2d.device)
+        h = run("grouped_swiglu", w4a16_stream_swiglu, xp_tok, xs_tok, st["gate_proj"], st["up_proj"], off_local,
+                st["group_size"], shuffle_out=False, status=status, perm=perm, top_k=K)
+        out_perm = run("grouped_down", w4a16_grouped_gemm, h, *st["down_proj"], off_local, st["group_size"],
+                       zero_init=False)
+        run("send_partials", peer.send_partials, out_perm, weights, ids32, inv, T, K, el)   # barrier inside
+        return run("sum_partials", peer.sum_partials, T, res)
+
+    def _forward_peer(self, x2d, st, weights, ids32, perm, inv, off32, T, K, E, res=None):
+        """Expert-parallel path over peer memory: rows go straight from x into the owners' receive
+        buffers and expert outputs are read straight from the owners while combining."""
+        run = self._stage
+        peer = self._ensure_peer(x2d, T, K)
+        if st["w4"] and self.ep_size * T <= self.fuse_max_tokens:
+            # a decode batch on the dispatch path: a block keeps to ONE of the two decode paths (they lay the peer
+            # buffers out differently, and switching between them on a live block is not supported)
+            self._decode_mode_used = self._decode_mode_used or "dispatch"
+            if self._decode_mode_used != "dispatch":
+                raise RuntimeError("this block has run decode batches by replication; ep_decode cannot change afterwards")
         tc5 = (not st["w4"]) and scatter_gemm_supported(peer.recv_rows(), st["w2"]) \
             and gather_swiglu_supported(peer.recv_rows(), st["w13"])
         fused_return = tc5 and self.ep_return == "fused"

@@ -129,6 +129,7 @@ class PeerExchange:
         self.recv_ptrs = torch.tensor(list(h_recv.buffer_ptrs), dtype=torch.int64, device=device)
         self.y_ptrs = torch.tensor(list(h_y.buffer_ptrs), dtype=torch.int64, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._done = None              # counter of the partial-sum kernel (decode by replication)
         self._tab = None               # symmetric int32 [2, cap_rows]: slot table and home table
         self._counts = None            # symmetric [G, E] int32, created on first use (E is not known here)
         self._sig = symm_mem.empty(max(self.world, 32), dtype=torch.int32, device=device)
@@ -277,6 +278,48 @@ class PeerExchange:
                                     c.stream_ptr(weights.device))
         c.check(rc, "mq_ep_combine")
         c.count_launches(1 if num_tokens else 0)
+        return out
+
+    # ---- decode batches by replication: every rank holds all tokens, runs its own experts, sends partial sums
+    def gather_tokens(self, x: torch.Tensor) -> torch.Tensor:
+        """This rank's rows into every peer's token buffer, then the rank barrier; returns all tokens of the step,
+        [G*T, H] in rank order (a view of the receive buffer).  Every rank must pass the same number of rows."""
+        T, H = x.shape
+        if self.world * T > self.cap_rows or H != self.hidden or x.dtype != self.dtype:
+            raise ValueError("token buffer too small or of another shape / dtype")
+        c = self._cabi
+        rc = c.load().mq_ep_gather_tokens(c.ptr(x), c.dtype_code(x), T, H, self.world, self.rank, c.ptr(self.recv_ptrs),
+                                          c.ptr(self.sig_ptrs), c.ptr(self._epoch), self.max_polls, c.ptr(self.status),
+                                          c.stream_ptr(x.device))
+        c.check(rc, "mq_ep_gather_tokens")
+        c.count_launches(1)
+        return self.recv.view(self.cap_rows, self.hidden)[: self.world * T]
+
+    def send_partials(self, rows, weights, ids32, inv, tokens_per_rank: int, top_k: int, experts_per_rank: int) -> None:
+        """Every token's partial weighted sum over this rank's slots goes, in fp32, to the rank that owns the
+        token (into its expert-output buffer, read as fp32); then the rank barrier."""
+        T, G = tokens_per_rank, self.world
+        if G * T * self.hidden * 4 > self.cap_rows * self.hidden * self.y.element_size():
+            raise ValueError("partial-sum buffer too small")
+        if self._done is None:
+            self._done = torch.zeros(1, dtype=torch.int32, device=rows.device)
+        c = self._cabi
+        rc = c.load().mq_ep_send_partials(c.ptr(rows), c.dtype_code(rows), c.ptr(weights), c.ptr(ids32), c.ptr(inv),
+                                          G * T, top_k, self.hidden, T, G, self.rank, experts_per_rank,
+                                          c.ptr(self.y_ptrs), c.ptr(self._done), c.ptr(self.sig_ptrs), c.ptr(self._epoch),
+                                          self.max_polls, c.ptr(self.status), c.stream_ptr(rows.device))
+        c.check(rc, "mq_ep_send_partials")
+        c.count_launches(1)
+
+    def sum_partials(self, tokens_per_rank: int, residual=None) -> torch.Tensor:
+        """This rank's tokens: the G partial sums added in rank order, cast (and the layer's residual added)."""
+        T = tokens_per_rank
+        out = torch.empty(T, self.hidden, dtype=self.dtype, device=self.y.device)
+        c = self._cabi
+        rc = c.load().mq_ep_sum_partials(c.ptr(self.y), c.dtype_code(out), c.ptr(residual), T, self.hidden, self.world,
+                                         c.ptr(out), c.stream_ptr(out.device))
+        c.check(rc, "mq_ep_sum_partials")
+        c.count_launches(1)
         return out
 
     def check_status(self) -> None:

@@ -19,6 +19,9 @@ SHAPES = {
     "small": (300, 512, 16, 4, 256, 2.0),
     # the benchmark layer: 128 experts, top-8, H=2048, I=768 (16 experts per rank on 8 GPUs)
     "layer": (512, 2048, 128, 8, 768, 1.0),
+    # a decode step of that layer: few enough tokens that W4A16 blocks go by replication (every rank holds all
+    # tokens, runs its own experts and sends partial sums) instead of dispatching rows
+    "decode": (4, 2048, 128, 8, 768, 1.0),
 }
 
 
@@ -101,7 +104,12 @@ def _worker(rank, world, port, w4, mode, shape):
             ref, ref_ids, _, _ = O.block_forward(lay.x[sl], lay.router, lay.gate, lay.up, lay.down, K, True, bias)
         blk.router_bias = bias.to(dev)
         x = lay.x[sl].to(dev)
+
+        def mark(step):                                       # which step a rank had completed, in the test's log
+            torch.cuda.synchronize()
+            print(f"[rank {rank}] {shape}: {step} done", file=sys.stderr, flush=True)
         out = blk(x)
+        mark("first forward")
         ids, _ = moe_router(x, router_w.to(dev), K, bias=bias.to(dev))
         go = agree.check(torch.equal(ids.cpu(), ref_ids), f"rank {rank}: expert ids differ from the oracle")
         want, got = ref.float(), out.cpu().float()
@@ -119,6 +127,7 @@ def _worker(rank, world, port, w4, mode, shape):
         go = agree.check(ok, msg) and go
         if go:
             go = agree.check(torch.equal(blk(x), out), f"rank {rank}: not deterministic across calls")
+            mark("second forward")
         if go and mode == "p2p":
             status_ok = True
             try:
@@ -136,12 +145,16 @@ def _worker(rank, world, port, w4, mode, shape):
                 go = agree.check(torch.equal(blk(x), out), f"rank {rank}: {ret}/{disp} differs")
             if go:
                 from mini_qwen_b200.graph import CapturedForward
+                mark("dispatch / return variants")
                 cap = CapturedForward(blk, x)                 # collective: every rank captures and replays
                 same = torch.equal(cap.replay(), out) and torch.equal(cap.replay(), out)
                 go = agree.check(same, f"rank {rank}: graph replay differs")
+                mark("graph replays")
             if go:
-                out_small = blk(x[:17])                       # fewer tokens than the buffers were sized for
-                go = agree.check(tuple(out_small.shape) == (17, H), f"rank {rank}: short batch shape")
+                n_small = min(17, max(1, T_local // 2))       # fewer tokens than the buffers were sized for
+                out_small = blk(x[:n_small])
+                go = agree.check(tuple(out_small.shape) == (n_small, H), f"rank {rank}: short batch shape")
+                mark("short batch")
         torch.cuda.synchronize()
         dist.barrier()                                        # nobody leaves while kernels are in flight anywhere
     finally:
@@ -162,6 +175,15 @@ def test_expert_parallel_block_matches_oracle(w4, mode):
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
     mp.spawn(_worker, args=(world, _free_port(), w4, mode, "small"), nprocs=world, join=True)
+
+
+def test_expert_parallel_w4a16_decode_step_by_replication():
+    """A decode step (4 tokens per rank) of the W4A16 benchmark layer: the block gathers all tokens on every rank,
+    runs each rank's own experts and adds the partial sums up at the tokens' owners."""
+    world = _world()
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mp.spawn(_worker, args=(world, _free_port(), True, "p2p", "decode"), nprocs=world, join=True)
 
 
 def test_expert_parallel_layer_shape_on_all_gpus():
