@@ -184,3 +184,20 @@ def test_ep_entry_points_reject_bad_poll_budgets_without_a_gpu():
     assert lib.mq_stack_tensors(None, 3, 64, 1, None, None) == 1                     # null pointers
     assert lib.mq_stack_tensors(None, 0, 64, 1, None, None) == 0                     # nothing to do
     assert lib.mq_stack_tensors(None, 70000, 64, 1, None, None) == 1
+
+
+def test_decode_replication_entry_points_reject_bad_arguments_without_a_gpu():
+    lib = _cabi.load()
+    assert lib.mq_ep_gather_tokens(None, 1, 4, 2048, 2, 0, None, None, None, 0, None, None) == 1     # null pointers
+    assert lib.mq_ep_gather_tokens(None, 1, 4, 2048, 2, 2, None, None, None, 0, None, None) == 1     # rank >= G
+    assert lib.mq_ep_gather_tokens(None, 1, 4, 2047, 2, 0, None, None, None, 0, None, None) == 2     # rows not 16-byte multiples
+    # tokens must be G * T
+    assert lib.mq_ep_send_partials(None, 1, None, None, None, 9, 8, 2048, 4, 2, 0, 64, None, None, None, None, 0,
+                                   None, None) == 1
+    assert lib.mq_ep_send_partials(None, 1, None, None, None, 8, 33, 2048, 4, 2, 0, 64, None, None, None, None, 0,
+                                   None, None) == 2                                             # K > 32
+    assert lib.mq_ep_sum_partials(None, 1, None, 4, 2048, 2, None, None) == 1                        # null pointers
+    assert lib.mq_ep_sum_partials(None, 1, None, 4, 2046, 2, None, None) == 2                        # H not a multiple of 4
+    assert lib.mq_rms_norm(None, 1, None, 1e-6, 4, 2048, None, None) == 1                            # null pointers
+    assert lib.mq_rms_norm(None, 1, None, 1e-6, 0, 2048, None, None) == 0                            # nothing to do
+    assert lib.mq_unpermute_combine_residual(None, 1, None, None, None, 4, 33, 64, None, None) == 2  # K > 32
