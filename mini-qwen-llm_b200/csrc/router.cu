@@ -751,8 +751,11 @@ extern "C" int mq_route_small(const void* x, int x_dtype, const void* w, int w_d
   if (workspace_bytes < mq_route_small_workspace_bytes(T, E) || !aligned16(workspace)) return MQ_ERR_WORKSPACE_TOO_SMALL;
   if (xp != nullptr && (!aligned16(x) || !aligned16(xp))) return MQ_ERR_INVALID_ARGUMENT;
   const int vec_ok = (H % 8 == 0) && aligned16(x) && aligned16(w);
-  float* logits = reinterpret_cast<float*>(workspace);
-  int* counter = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + (size_t)T * E * sizeof(float));
+  // The counter sits at the START of the workspace, the logits behind it: its place must not depend on T, or a
+  // call with fewer tokens than an earlier one on the same workspace would find the earlier call's logits where
+  // it expects a zero counter (no CTA would then be "last" and the plan would never be written).
+  int* counter = reinterpret_cast<int*>(workspace);
+  float* logits = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + 16);
   const size_t smem = (size_t)E * 8 + (size_t)T * E * 4 + (size_t)T * K * 4 + (size_t)E * 4;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define MQ_RSM_LAUNCH(EPL)                                                                                       \

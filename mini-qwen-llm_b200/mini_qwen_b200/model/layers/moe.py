@@ -95,7 +95,6 @@ class Qwen3MoEBlock(nn.Module):
         # expert-parallel W4A16 decode batches (at most 64 tokens over all ranks): "replicate" = every rank holds
         # all tokens and runs its own experts (two rank barriers per call), "dispatch" = the prefill path
         self.ep_decode = "replicate"
-        self._decode_mode_used = None
         self._route_ws = None
         self._peer = None
         self.ep_size = 1 if ep_group is None else torch.distributed.get_world_size(ep_group)
@@ -396,9 +395,6 @@ class Qwen3MoEBlock(nn.Module):
         fp32 sums of the combine."""
         run = self._stage
         peer = self._ensure_peer(x2d, T, K)
-        self._decode_mode_used = self._decode_mode_used or "replicate"
-        if self._decode_mode_used != "replicate":
-            raise RuntimeError("this block has run decode batches by dispatch; ep_decode cannot change afterwards")
         G, el = self.ep_size, E // self.ep_size
         x_all = run("gather_tokens", peer.gather_tokens, x2d)                        # [G*T, H], barrier inside
         if self._route_ws is None or self._route_ws.device != x2d.device:
@@ -422,12 +418,6 @@ class Qwen3MoEBlock(nn.Module):
         buffers and expert outputs are read straight from the owners while combining."""
         run = self._stage
         peer = self._ensure_peer(x2d, T, K)
-        if st["w4"] and self.ep_size * T <= self.fuse_max_tokens:
-            # a decode batch on the dispatch path: a block keeps to ONE of the two decode paths (they lay the peer
-            # buffers out differently, and switching between them on a live block is not supported)
-            self._decode_mode_used = self._decode_mode_used or "dispatch"
-            if self._decode_mode_used != "dispatch":
-                raise RuntimeError("this block has run decode batches by replication; ep_decode cannot change afterwards")
         tc5 = (not st["w4"]) and scatter_gemm_supported(peer.recv_rows(), st["w2"]) \
             and gather_swiglu_supported(peer.recv_rows(), st["w13"])
         fused_return = tc5 and self.ep_return == "fused"

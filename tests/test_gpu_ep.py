@@ -166,6 +166,19 @@ def _worker(rank, world, port, w4, mode, shape):
                 out_small = blk(x[:n_small])
                 go = agree.check(tuple(out_small.shape) == (n_small, H), f"rank {rank}: short batch shape")
                 mark("short batch")
+            if go and w4 and shape == "decode":
+                # the dispatch path on the same step: the same experts' outputs, the combine's sums in another order
+                blk.ep_decode = "dispatch"
+                other = blk(x)
+                blk.ep_decode = "replicate"
+                close = bool(((other.float() - out.float()).abs() <= 2e-2 * out.float().abs() + 2e-3).float().mean() >= 0.995)
+                go = agree.check(close, f"rank {rank}: dispatch and replication disagree")
+                mark("dispatch path on the same step")
+                # and the shorter batch again, against its rows of the full step (same routing, same experts)
+                again = blk(x[:n_small])
+                same = bool(((again.float() - out[:n_small].float()).abs()
+                             <= 2e-2 * out[:n_small].float().abs() + 2e-3).float().mean() >= 0.995)
+                go = agree.check(same, f"rank {rank}: the short batch differs from its rows of the full step")
         torch.cuda.synchronize()
         dist.barrier()                                        # nobody leaves while kernels are in flight anywhere
     finally:

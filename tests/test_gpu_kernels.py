@@ -382,3 +382,23 @@ def test_fused_small_batch_routing_equals_the_separate_kernels_and_the_oracle(T,
                                      renormalize=renorm, return_int32_ids=True)
     assert torch.equal(ids32_b, ids32)
     torch.testing.assert_close(w_b, wts, rtol=1e-5, atol=1e-7)
+
+
+def test_fused_routing_workspace_is_reusable_across_batch_sizes():
+    """One workspace, batches of 64, then 8, then 1, then 33 tokens: the kernel's counter must not sit where an
+    earlier, larger batch left its logits (it once did: no CTA then took the plan step and the outputs of the
+    smaller batch were never written)."""
+    from mini_qwen_b200.kernels.moe_router import moe_route_small, route_small_workspace
+    E, K, H = 128, 8, 2048
+    g = torch.Generator().manual_seed(5)
+    w = (torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16)
+    ws = route_small_workspace(E, DEV)
+    for T in (64, 8, 1, 33, 2):
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        ids32, wts, perm, inv, off32, _, _ = moe_route_small(x.to(DEV), w.to(DEV), K, renormalize=True, workspace=ws)
+        ref_ids, ref_w = O.router(x, w, K, None)
+        assert torch.equal(cpu(ids32).to(torch.int64), ref_ids), f"T={T}"
+        ref_perm, ref_inv = O.sort_slots(ref_ids)
+        assert torch.equal(cpu(perm).to(torch.int64), ref_perm) and torch.equal(cpu(inv).to(torch.int64), ref_inv)
+        assert torch.equal(cpu(off32).to(torch.int64), O.expert_offsets(ref_ids, E))
+        torch.testing.assert_close(cpu(wts), O.renormalise(ref_w), rtol=1e-4, atol=1e-6)
