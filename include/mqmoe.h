@@ -99,8 +99,8 @@ int mq_router_topk_static(const void* x, int x_dtype, const void* w, int w_dtype
  * layer call is bound by its chain of launches.  Same ids, weights, perm, inv and offsets as mq_router_topk
  * followed by mq_permute_plan (the logits are summed in the order of the few-token logits kernel).
  *   workspace: mq_route_small_workspace_bytes(T, E) bytes, 16-byte aligned, ZERO-FILLED ONCE by the caller
- *     after allocating it (it holds a counter the kernel leaves at zero again, in its first 16 bytes, and the
- *     logits behind it); calls that share a workspace may differ in T and must not overlap on the GPU;
+ *     after allocating it (it holds counters the kernel leaves at zero again, in its first 512 bytes, and the
+ *     logits behind them); calls that share a workspace may differ in T and must not overlap on the GPU;
  *   ids32 int32 [T,K] (required), ids64 int64 [T,K] (optional), weights fp32 [T,K], perm/inv int32 [T*K],
  *     offsets64 / offsets32 [E+1] (one may be NULL);
  *   xp [T,H] (16-bit) and xs fp32 [T,32], both or neither: every token row in the k order 0,4,1,5,2,6,3,7

@@ -368,6 +368,201 @@ router_softmax_topk(const float* __restrict__ logits, int slices, const float* _
 constexpr int RSM_THREADS = 512;
 constexpr int RSM_MAX_T = 64, RSM_MAX_E = 256, RSM_MAX_S = 2048;
 
+// The plan of a small batch (a stable counting sort of the T*K slots by expert), by all threads of one CTA.  A
+// token's K experts are distinct and the slots are token-major, so the rank of slot (t, k) inside its expert is
+// the number of earlier TOKENS that chose the expert: with T <= 64 one 64-bit mask per expert holds everything,
+// and no step is serial.  s_ids [T*K] holds the ids; s_mask [E] must be zero on entry; s_run [E] is scratch.
+__device__ void route_plan_small(const int* s_ids, unsigned long long* s_mask, int* s_run, int T, int E, int K,
+                                 int32_t* __restrict__ ids32, int32_t* __restrict__ perm, int32_t* __restrict__ inv,
+                                 int32_t* __restrict__ off32, int64_t* __restrict__ off64) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+  const int S = T * K;
+  for (int i = tid; i < S; i += nthreads) {
+    const int ee = s_ids[i];
+    if (ids32 != nullptr) ids32[i] = ee;
+    atomicOr(&s_mask[ee], 1ull << (i / K));
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // exclusive scan of the E counts: each lane takes E/32 (at most 8) consecutive experts
+    const int per = (E + 31) / 32;
+    int cnt[RSM_MAX_E / 32];
+    int sum = 0;
+#pragma unroll
+    for (int j = 0; j < RSM_MAX_E / 32; ++j) {
+      const int ee = lane * per + j;
+      cnt[j] = (j < per && ee < E) ? __popcll(s_mask[ee]) : 0;
+      sum += cnt[j];
+    }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int j = 0; j < RSM_MAX_E / 32; ++j) {
+      const int ee = lane * per + j;
+      if (j < per && ee < E) {
+        s_run[ee] = run;
+        if (off64) off64[ee] = run;
+        if (off32) off32[ee] = run;
+      }
+      run += cnt[j];
+    }
+    if (lane == 31) {
+      if (off64) off64[E] = incl;
+      if (off32) off32[E] = incl;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < S; i += nthreads) {
+    const int ee = s_ids[i];
+    const int t = i / K;
+    const int pos = s_run[ee] + __popcll(s_mask[ee] & ((1ull << t) - 1ull));
+    perm[pos] = i;
+    inv[i] = pos;
+  }
+}
+
+// The activation preparation of one token row (w4_prep.cuh) by all threads of a CTA; s_red: a float per warp.
+__device__ void route_prepare_row(const __nv_bfloat16* __restrict__ x_row, int H, int prep_mode,
+                                  __nv_bfloat16* __restrict__ xp_row, float* __restrict__ xs_row, float* s_red) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
+  const uint4* in = reinterpret_cast<const uint4*>(x_row);
+  uint4* o = reinterpret_cast<uint4*>(xp_row);
+  const bool f16 = prep_mode == 2;
+  float scale = 1.0f;
+  if (f16) {
+    float amax = 0.0f;
+    for (int c = tid; c < H / 8; c += nthreads) amax = fmaxf(amax, w4_piece_amax(in[c]));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    __syncthreads();
+    if (lane == 0) s_red[warp] = amax;
+    __syncthreads();
+    amax = 0.0f;
+    for (int wi = 0; wi < nthreads / 32; ++wi) amax = fmaxf(amax, s_red[wi]);
+    const int ex = w4_row_exponent(amax);
+    scale = w4_pow2(ex);
+    if (tid == 0) xs_row[W4_XS_UNSCALE] = w4_pow2(-ex);
+  }
+  for (int c0 = warp * 32; c0 < H / 8; c0 += nthreads) {
+    const int c = c0 + lane;
+    float sum = 0.0f;
+    if (c < H / 8) o[c] = w4_prepare_piece(in[c], true, f16, scale, sum);
+#pragma unroll
+    for (int d = 8; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    if ((lane & 15) == 0 && c < H / 8) xs_row[c >> 4] = sum;
+  }
+}
+
+// ---- the same for batches of more than 16 tokens, laid out by TOKEN: CTA (eg, t) forms the logits of experts
+// [32 eg, 32 eg + 32) for token t (a warp takes four experts; a lane keeps its pieces of the token's row in
+// registers; all loads of a lane are independent: one round trip), the CTA that arrives last on token t's counter
+// does that token's softmax and top-k (one warp), and the CTA that finishes the last token makes the plan.  The
+// selection of the tokens thus runs on as many SMs as there are tokens instead of on one.  16-bit x and w only.
+constexpr int RTK_THREADS = 256;
+constexpr int RTK_HEADER_INTS = 128;                  // workspace header: counter of the narrow kernel, all-tokens
+                                                      // counter, one counter per token (64)
+template <int EPL>
+__global__ void __launch_bounds__(RTK_THREADS)
+route_tokens_kernel(const uint16_t* __restrict__ x, int x_bf16, const uint16_t* __restrict__ w, int w_bf16,
+                    const float* __restrict__ bias, int T, int H, int E, int K, int renorm,
+                    float* __restrict__ logits, int* __restrict__ header,
+                    int32_t* __restrict__ ids32, int64_t* __restrict__ ids64, float* __restrict__ weights,
+                    int32_t* __restrict__ perm, int32_t* __restrict__ inv, int32_t* __restrict__ off32,
+                    int64_t* __restrict__ off64, __nv_bfloat16* __restrict__ xp, float* __restrict__ xs,
+                    int prep_mode) {
+  extern __shared__ __align__(16) uint8_t rtk_smem[];
+  __shared__ int s_last;
+  __shared__ float s_red[RTK_THREADS / 32];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int eg = blockIdx.x, t = blockIdx.y, groups = gridDim.x;
+  int* all_ctr = header + 1;
+  int* tok_ctr = header + 2;
+  pdl_wait();
+  pdl_release();
+
+  // ---- logits: warp `warp` takes experts e0 .. e0+3; a lane's pieces of the row: k = 8 (lane + 32 i)
+  {
+    constexpr int MAXP = 8;                            // pieces per lane kept in registers (H <= 2048); more: re-read
+    const int pieces = H / 8;
+    const uint16_t* xr = x + (size_t)t * H;
+    const int e0 = eg * 32 + warp * 4;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int p0 = 0; p0 < pieces; p0 += 32 * MAXP) {
+      uint4 xv[MAXP];
+#pragma unroll
+      for (int i = 0; i < MAXP; ++i) {
+        const int pc = p0 + lane + 32 * i;
+        xv[i] = pc < pieces ? __ldg(reinterpret_cast<const uint4*>(xr) + pc) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + j;
+        if (e < E) {
+          const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)e * H);
+          uint4 wv[MAXP];
+#pragma unroll
+          for (int i = 0; i < MAXP; ++i) {
+            const int pc = p0 + lane + 32 * i;
+            wv[i] = pc < pieces ? __ldg(wr + pc) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int i = 0; i < MAXP; ++i) {
+            float a[8], b[8];
+            unpack8_16bit(xv[i], x_bf16 != 0, a);
+            unpack8_16bit(wv[i], w_bf16 != 0, b);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[j] = fmaf(a[q], b[q], acc[j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float v = acc[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && e0 + j < E) logits[(size_t)t * E + e0 + j] = v;
+    }
+  }
+  if (xp != nullptr && eg == 0)
+    route_prepare_row(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)t * H, H, prep_mode, xp + (size_t)t * H,
+                      xs + (size_t)t * W4_XS_STRIDE, s_red);
+
+  // ---- last on this token?
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(&tok_ctr[t], 1) == groups - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  unsigned long long* s_mask = reinterpret_cast<unsigned long long*>(rtk_smem);   // [E]
+  float* s_logits = reinterpret_cast<float*>(s_mask + E);                        // [E]
+  int* s_ids = reinterpret_cast<int*>(s_logits + E);                             // [T * K]
+  int* s_run = s_ids + T * K;                                                    // [E]
+  for (int i = tid; i < E; i += RTK_THREADS) s_logits[i] = __ldcg(logits + (size_t)t * E + i);
+  __syncthreads();
+  if (warp == 0)
+    softmax_topk_row<EPL>(s_logits, 1, 0, bias, E, K, renorm, lane, ids64 ? ids64 + (size_t)t * K : nullptr,
+                          ids32 + (size_t)t * K, weights + (size_t)t * K);
+  // ---- last of the tokens?
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(all_ctr, 1) == T - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int ee = tid; ee < E; ee += RTK_THREADS) s_mask[ee] = 0ull;
+  for (int i = tid; i < T * K; i += RTK_THREADS) s_ids[i] = __ldcg(ids32 + i);
+  __syncthreads();
+  route_plan_small(s_ids, s_mask, s_run, T, E, K, nullptr, perm, inv, off32, off64);
+  for (int i = tid; i < T + 1; i += RTK_THREADS) header[1 + i] = 0;              // ready for the next call
+}
+
 template <int EPL>
 __global__ void __launch_bounds__(RSM_THREADS)
 route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__ w, int wdt,
@@ -510,58 +705,8 @@ route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__
     }
   }
   __syncthreads();
-  // The plan (a stable counting sort of the T*K slots by expert).  A token's K experts are distinct and the
-  // slots are token-major, so the rank of slot (t, k) inside its expert is the number of earlier TOKENS that
-  // chose the expert: with T <= 64 one 64-bit mask per expert holds everything, and no step is serial.
-  const int S = T * K;
-  for (int i = tid; i < S; i += RSM_THREADS) {
-    const int ee = s_ids[i];
-    ids32[i] = ee;
-    atomicOr(&s_mask[ee], 1ull << (i / K));
-  }
-  __syncthreads();
-  if (warp == 0) {
-    // exclusive scan of the E counts: each lane takes E/32 (at most 8) consecutive experts
-    const int per = (E + 31) / 32;
-    int cnt[RSM_MAX_E / 32];
-    int sum = 0;
-#pragma unroll
-    for (int j = 0; j < RSM_MAX_E / 32; ++j) {
-      const int ee = lane * per + j;
-      cnt[j] = (j < per && ee < E) ? __popcll(s_mask[ee]) : 0;
-      sum += cnt[j];
-    }
-    int incl = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += n;
-    }
-    int run = incl - sum;
-#pragma unroll
-    for (int j = 0; j < RSM_MAX_E / 32; ++j) {
-      const int ee = lane * per + j;
-      if (j < per && ee < E) {
-        s_run[ee] = run;
-        if (off64) off64[ee] = run;
-        if (off32) off32[ee] = run;
-      }
-      run += cnt[j];
-    }
-    if (lane == 31) {
-      if (off64) off64[E] = incl;
-      if (off32) off32[E] = incl;
-      *counter = 0;                                 // ready for the next call
-    }
-  }
-  __syncthreads();
-  for (int i = tid; i < S; i += RSM_THREADS) {
-    const int ee = s_ids[i];
-    const int t = i / K;
-    const int pos = s_run[ee] + __popcll(s_mask[ee] & ((1ull << t) - 1ull));
-    perm[pos] = i;
-    inv[i] = pos;
-  }
+  route_plan_small(s_ids, s_mask, s_run, T, E, K, ids32, perm, inv, off32, off64);
+  if (tid == 0) *counter = 0;                       // ready for the next call
 }
 
 template <int EPL>
@@ -727,7 +872,7 @@ extern "C" int mq_router_topk_static(const void* x, int x_dtype, const void* w, 
 // ---------------------------------------------------------------------------------------------
 extern "C" size_t mq_route_small_workspace_bytes(int64_t T, int64_t E) {
   if (T <= 0 || E <= 0) return 16;
-  return (size_t)T * (size_t)E * sizeof(float) + 16;
+  return (size_t)T * (size_t)E * sizeof(float) + 512;       // a header of counters, then the logits
 }
 
 extern "C" int mq_route_small(const void* x, int x_dtype, const void* w, int w_dtype, const float* bias,
@@ -751,13 +896,31 @@ extern "C" int mq_route_small(const void* x, int x_dtype, const void* w, int w_d
   if (workspace_bytes < mq_route_small_workspace_bytes(T, E) || !aligned16(workspace)) return MQ_ERR_WORKSPACE_TOO_SMALL;
   if (xp != nullptr && (!aligned16(x) || !aligned16(xp))) return MQ_ERR_INVALID_ARGUMENT;
   const int vec_ok = (H % 8 == 0) && aligned16(x) && aligned16(w);
-  // The counter sits at the START of the workspace, the logits behind it: its place must not depend on T, or a
-  // call with fewer tokens than an earlier one on the same workspace would find the earlier call's logits where
-  // it expects a zero counter (no CTA would then be "last" and the plan would never be written).
+  // The counters sit at the START of the workspace (a header of 128 ints), the logits behind them: their place
+  // must not depend on T, or a call with fewer tokens than an earlier one on the same workspace would find the
+  // earlier call's logits where it expects zero counters (no CTA would then be "last" and the plan would never
+  // be written).
   int* counter = reinterpret_cast<int*>(workspace);
-  float* logits = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + 16);
-  const size_t smem = (size_t)E * 8 + (size_t)T * E * 4 + (size_t)T * K * 4 + (size_t)E * 4;
+  float* logits = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + RTK_HEADER_INTS * sizeof(int));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (T > 16 && vec_ok && x_dtype != MQ_F32 && w_dtype != MQ_F32) {
+    // more tokens than one CTA has warps: the token-major kernel (selection on as many SMs as there are tokens)
+    const size_t smem_t = (size_t)E * 8 + (size_t)E * 4 + (size_t)T * K * 4 + (size_t)E * 4;
+    const dim3 grid((unsigned)((E + 31) / 32), (unsigned)T);
+#define MQ_RTK_LAUNCH(EPL)                                                                                       \
+    launch_after_predecessor(route_tokens_kernel<EPL>, grid, dim3(RTK_THREADS), smem_t, st,                       \
+        reinterpret_cast<const uint16_t*>(x), (int)(x_dtype == MQ_BF16), reinterpret_cast<const uint16_t*>(w),    \
+        (int)(w_dtype == MQ_BF16), bias, (int)T, (int)H, (int)E, (int)K, renormalize, logits, counter, ids32,     \
+        ids64, weights, perm, inv, offsets32, offsets64, reinterpret_cast<__nv_bfloat16*>(xp), xs,                \
+        xp_format == 2 ? 2 : 1)
+    if (E <= 32) MQ_RTK_LAUNCH(1);
+    else if (E <= 64) MQ_RTK_LAUNCH(2);
+    else if (E <= 128) MQ_RTK_LAUNCH(4);
+    else MQ_RTK_LAUNCH(8);
+#undef MQ_RTK_LAUNCH
+    return check_launch();
+  }
+  const size_t smem = (size_t)E * 8 + (size_t)T * E * 4 + (size_t)T * K * 4 + (size_t)E * 4;
 #define MQ_RSM_LAUNCH(EPL)                                                                                       \
   do {                                                                                                           \
     cudaFuncSetAttribute(route_small_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
