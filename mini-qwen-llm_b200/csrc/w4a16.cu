@@ -40,6 +40,12 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc)
                : "memory");
 }
+// the same through L1: for the activation pieces, which the four warps of a CTA (four column tiles, the same rows and
+// k) all fetch within a few hundred cycles of one another (down projection at batch 64: 38.5 -> 36.6 us)
+__device__ __forceinline__ void cp_async16_l1(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -241,7 +247,7 @@ w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
         uint4* sl = ring_lane + i * SLOT_STRIDE;
         cp_async16(sl, qw[0] + w_off);
         cp_async16(sl + 32, qw[1] + w_off);
-        cp_async16(sl + 64, xrow + x_off);
+        cp_async16_l1(sl + 64, xrow + x_off);
       }
       cp_async_commit();
       w_off += 4u * (uint32_t)N;
@@ -271,7 +277,7 @@ w4a16_grouped_kernel(const __nv_bfloat16* __restrict__ x, W4Proj p0, W4Proj p1,
       if (fetch < s_hi) {                              // refill the slot just read
         cp_async16(sl, qw[0] + w_off);
         cp_async16(sl + 32, qw[1] + w_off);
-        cp_async16(sl + 64, xrow + x_off);
+        cp_async16_l1(sl + 64, xrow + x_off);
       }
       cp_async_commit();
       w_off += 4u * (uint32_t)N;

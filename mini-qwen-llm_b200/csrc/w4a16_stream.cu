@@ -166,9 +166,12 @@ __device__ __forceinline__ void ws_mma(float (&c)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
   }
 }
+// Activation pieces: read-only path, allocating in L1 (the warps that share a K slice read the same pieces within a
+// few hundred cycles of one another; with L1::no_allocate every one of them went to L2: 69.6 against 67.7 us on
+// the batch-64 gate/up launch).
 __device__ __forceinline__ uint4 ws_ldg128(const void* p) {
   uint4 v;
-  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
       : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
