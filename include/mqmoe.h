@@ -96,8 +96,10 @@ int mq_router_topk_static(const void* x, int x_dtype, const void* w, int w_dtype
  * Router + permute plan (+ activation preparation) for small batches, in one launch.  Replaces, for decode
  * batches, the chain moe_router -> renormalise -> index work of moe_permute (mini_qwen/model/layers/moe.py:
  * 54-57) that the calls above and below make in three launches (plus mq_w4a16_tc_prep): at these sizes the
- * layer call is bound by its chain of launches.  Same ids, weights, perm, inv and offsets as mq_router_topk
- * followed by mq_permute_plan (the logits are summed in the order of the few-token logits kernel).
+ * layer call is bound by its chain of launches.  Same ids, perm, inv and offsets as mq_router_topk followed
+ * by mq_permute_plan; the weights can differ from that chain's in the last place (the fp32 logit sums run in
+ * another order).  Up to 16 tokens: a CTA per expert, the last CTA selects and plans; 17 to 64 tokens with
+ * 16-bit x and w: a CTA per (32 experts, token), the last CTA of a token selects, the last token's CTA plans.
  *   workspace: mq_route_small_workspace_bytes(T, E) bytes, 16-byte aligned, ZERO-FILLED ONCE by the caller
  *     after allocating it (it holds counters the kernel leaves at zero again, in its first 512 bytes, and the
  *     logits behind them); calls that share a workspace may differ in T and must not overlap on the GPU;
