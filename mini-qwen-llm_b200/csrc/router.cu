@@ -642,36 +642,11 @@ route_small_kernel(const void* __restrict__ x, int xdt, const void* __restrict__
       logits[(size_t)tid * E + e] = v;
     }
   }
-  // ---- phase A: token row e prepared for the W4A16 kernels (w4_prep.cuh: the k order 0,4,1,5,2,6,3,7 inside
-  // every 8, bf16 as it is or fp16 scaled by the row's power of two) and its sums over every 128 k
+  // ---- phase A: token row e prepared for the W4A16 kernels (w4_prep.cuh), with its sums over every 128 k
   if (xp != nullptr && e < T) {
-    const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)e * H);
-    uint4* o = reinterpret_cast<uint4*>(xp + (size_t)e * H);
-    const bool f16 = prep_mode == 2;
-    float scale = 1.0f;
-    if (f16) {
-      float amax = 0.0f;
-      for (int c = tid; c < H / 8; c += RSM_THREADS) amax = fmaxf(amax, w4_piece_amax(in[c]));
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-      __syncthreads();                           // s_part is free again: the logits were formed above
-      if (lane == 0) s_part[0][warp] = amax;
-      __syncthreads();
-      amax = 0.0f;
-#pragma unroll
-      for (int wi = 0; wi < RSM_THREADS / 32; ++wi) amax = fmaxf(amax, s_part[0][wi]);
-      const int ex = w4_row_exponent(amax);
-      scale = w4_pow2(ex);
-      if (tid == 0) xs[(size_t)e * W4_XS_STRIDE + W4_XS_UNSCALE] = w4_pow2(-ex);
-    }
-    for (int c0 = warp * 32; c0 < H / 8; c0 += RSM_THREADS) {
-      const int c = c0 + lane;
-      float sum = 0.0f;
-      if (c < H / 8) o[c] = w4_prepare_piece(in[c], true, f16, scale, sum);
-#pragma unroll
-      for (int d = 8; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-      if ((lane & 15) == 0 && c < H / 8) xs[(size_t)e * W4_XS_STRIDE + (c >> 4)] = sum;
-    }
+    __syncthreads();                             // s_part is free again: the logits were formed above
+    route_prepare_row(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)e * H, H, prep_mode, xp + (size_t)e * H,
+                      xs + (size_t)e * W4_XS_STRIDE, &s_part[0][0]);
   }
 
   // ---- who is last?
